@@ -30,7 +30,7 @@ class Architecture:
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 _PARTS: Dict[str, Dict[str, type]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "filter": {},
 }
 
 
@@ -67,20 +67,26 @@ def architecture_of(model_dir: str):
         raise ConfigError(f"{model_dir!r} holds no config.json")
     with open(path) as f:
         raw = json.load(f)
-    archs = raw.get("architectures")
-    if archs and isinstance(archs, list):
-        name = str(archs[0])
-    elif raw.get("model_type") in _MODEL_TYPES:
-        name = _MODEL_TYPES[raw["model_type"]]
-    else:
-        raise ConfigError("config.json has no 'architectures' list and no known 'model_type' "
-                          f"(known architectures: {sorted(_ARCHITECTURES)}; model types: {sorted(_MODEL_TYPES)})")
-    arch = architecture(name)
+    arch = architecture(architecture_name(raw))
     return arch, arch.parse_config(raw)
 
 
+def architecture_name(raw: dict) -> str:
+    """Which architecture a config.json means: the first of its ``architectures`` list, a single ``architecture``
+    string, or a known ``model_type``."""
+    archs = raw.get("architectures")
+    if archs and isinstance(archs, list):
+        return str(archs[0])
+    if isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
+    if raw.get("model_type") in _MODEL_TYPES:
+        return _MODEL_TYPES[raw["model_type"]]
+    raise ConfigError("config.json has no 'architectures' list, no 'architecture' and no known 'model_type' "
+                      f"(known architectures: {sorted(_ARCHITECTURES)}; model types: {sorted(_MODEL_TYPES)})")
+
+
 def register_part(family: str, kind: str, cls: type, *, replace: bool = False) -> None:
-    """family: 'mixer' | 'feed_forward' | 'norm' | 'position' | 'block' | 'embedding' | 'head'."""
+    """family: 'mixer' | 'feed_forward' | 'norm' | 'position' | 'block' | 'embedding' | 'head' | 'filter'."""
     if family not in _PARTS:
         raise ConfigError(f"unknown part family {family!r} (known: {sorted(_PARTS)})")
     if kind in _PARTS[family] and not replace:

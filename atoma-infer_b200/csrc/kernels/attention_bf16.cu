@@ -54,8 +54,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
                    const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
-                   int store_kv, int nq, int window, float scale_log2, int num_pages, int splits, int cluster_merge,
-                   int* __restrict__ status) {
+                   int store_kv, int nq, int window, int chunk, int sink, float scale_log2, int num_pages, int splits,
+                   int cluster_merge, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // tiles start on 1024-byte boundaries: TMA writes them with the 128-byte swizzle, whose pattern follows the address
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -80,7 +80,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     const int G = nq / L.num_kv_heads;
     const int row0 = e;
     const int kv_len = live ? newest + 1 : 0;
-    const int kstart = window > 0 ? max(0, kv_len - window) : 0;
+    int kstart = window > 0 ? max(0, kv_len - window) : 0;
+    if (chunk > 0 && live) kstart = max(kstart, newest - newest % chunk);  // only the keys of the newest position's chunk
     const int per = (((kv_len - kstart + splits - 1) / splits + DEC_KT - 1) / DEC_KT) * DEC_KT;
     const int lo = kstart + split * per, hi = min(kv_len, lo + per);
     const int* bt = meta + bt_offset + (size_t)e * bt_stride;
@@ -319,11 +320,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     __syncthreads();
     for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
         int r = idx / D, i = idx % D;
-        float mx = -INFINITY;
+        // the softmax's sink (a key of score 0 without a value) is one more partial result, of the first split
+        const bool with_sink = sink && split == 0;
+        float mx = with_sink ? 0.f : -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, mbuf[w * (32 + 16 * D) + r]);
         float lsum = 0.f, acc = 0.f;
         if (mx > -INFINITY) {
+            if (with_sink) lsum = fast_exp2(-mx);
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) {
                 const float* p = mbuf + w * (32 + 16 * D);
@@ -469,8 +473,8 @@ constexpr size_t PF_SMEM = (size_t)(PF_ROWS * LDS + PF_STAGES * 2 * PF_KT * LDS)
 __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
-                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, float scale_log2,
-                    int num_pages, int bt_cap, int* __restrict__ status) {
+                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, int chunk, int sink,
+                    float scale_log2, int num_pages, int bt_cap, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* kv = qtile + PF_ROWS * LDS;
@@ -498,7 +502,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
         *reinterpret_cast<uint4*>(qtile + toff(r, c * 8)) = v;
     }
     const int p_first = ctx + t0, p_last = p_first + nt - 1;
-    const int kbeg = window > 0 ? max(0, p_first - window + 1) : 0, kend = p_last + 1;
+    int kbeg = window > 0 ? max(0, p_first - window + 1) : 0;
+    if (chunk > 0) kbeg = max(kbeg, p_first - p_first % chunk);  // the first row's chunk starts earliest
+    const int kend = p_last + 1;
     const int k_first = (kbeg / PF_KT) * PF_KT;
     const int ntiles = (kend - k_first + PF_KT - 1) / PF_KT;
     const int page_lo = kbeg / L.page_size;
@@ -538,15 +544,19 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     const int warp_last_tok = min(nt - 1, warp_last_tok_all);
     const int warp_pmax = warp_first_tok < nt ? p_first + warp_last_tok : -1;
     const int warp_pmin = p_first + warp_first_tok;
-    const int warp_kmin = window > 0 ? max(0, p_first + warp_first_tok - window + 1) : 0;
+    int warp_kmin = window > 0 ? max(0, p_first + warp_first_tok - window + 1) : 0;
+    if (chunk > 0) warp_kmin = max(warp_kmin, warp_pmin - warp_pmin % chunk);
+    // with chunks: below this key some row of the warp sees nothing although the key is not after it
+    const int warp_cmax = chunk > 0 && warp_pmax >= 0 ? warp_pmax - warp_pmax % chunk : 0;
     const bool has_padding = warp_last_tok_all >= nt;
 
     float m[PF_MT][2], l[PF_MT][2];
     float o[PF_MT][DTILES][4];
 #pragma unroll
     for (int mt = 0; mt < PF_MT; ++mt) {
-        m[mt][0] = m[mt][1] = -INFINITY;
-        l[mt][0] = l[mt][1] = 0.f;
+        // with a sink the softmax has one more key, of score 0 and without a value: the running maximum and sum start there
+        m[mt][0] = m[mt][1] = sink ? 0.f : -INFINITY;
+        l[mt][0] = l[mt][1] = sink ? 1.f : 0.f;
 #pragma unroll
         for (int dt = 0; dt < DTILES; ++dt) o[mt][dt][0] = o[mt][dt][1] = o[mt][dt][2] = o[mt][dt][3] = 0.f;
     }
@@ -592,7 +602,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                 }
             }
             // only tiles that cross a row's last visible key (or a window's edge, or the range's ends) need a mask
-            const bool need_mask = has_padding || window > 0 || k0 + PF_KT - 1 > warp_pmin || k0 < kbeg;
+            const bool need_mask = has_padding || window > 0 || k0 + PF_KT - 1 > warp_pmin || k0 < kbeg || k0 < warp_cmax;
 #pragma unroll
             for (int mt = 0; mt < PF_MT; ++mt) {
 #pragma unroll
@@ -603,7 +613,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
                         if (need_mask) {
                             int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
                             int p = prow[mt][c >> 1];
-                            vis = key <= p && (window <= 0 || p - key < window);
+                            vis = key <= p && (window <= 0 || p - key < window) && (chunk <= 0 || key >= p - p % chunk);
                         }
                         s[mt][n][c] = vis ? s[mt][n][c] * scale_log2 : -INFINITY;
                     }
@@ -695,10 +705,12 @@ extern "C" int attn_decode_max_splits(int nq, int nkv) {
     return (int)(DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) / ((size_t)G * 2 * sizeof(float)));
 }
 
-extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                            const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
-                            int page_size, int num_pages, int window, float scale, int max_context, int* status,
-                            cudaStream_t stream) {
+// chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0);
+// sink: one more term in the softmax's denominator, a key of score 0 without a value.
+extern "C" int attn_prefill_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                   const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                                   int page_size, int num_pages, int window, int chunk, int sink, float scale, int max_context,
+                                   int* status, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
     if (nq % nkv || nq / nkv > 16) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
@@ -706,6 +718,7 @@ extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, cons
     dim3 grid((max_q_len + tpt - 1) / tpt, nkv, S);
     // block-table slice: the pages of the keys a tile can see (all of the context, or a window of it)
     int span = window > 0 ? min(max_context, window + tpt + PF_KT) : max_context;
+    if (chunk > 0) span = min(span, chunk + tpt + PF_KT);
     int bt_cap = span / page_size + 2;
     size_t smem = PF_SMEM + (size_t)bt_cap * sizeof(int);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
@@ -716,7 +729,16 @@ extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, cons
         configured = smem;
     }
     return (int)launch_kernel(attn_prefill_kernel, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L, meta,
-                              group, cu_tokens, ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
+                              group, cu_tokens, ctx_lens, (bf16*)out, nq, window, chunk, sink, scale * LOG2E, num_pages, bt_cap,
+                              status);
+}
+
+extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                            const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                            int page_size, int num_pages, int window, float scale, int max_context, int* status,
+                            cudaStream_t stream) {
+    return attn_prefill_masked(q, q_stride, cache, meta, group, cu_tokens, ctx_lens, out, S, max_q_len, nq, nkv, page_size,
+                               num_pages, window, 0, 0, scale, max_context, status, stream);
 }
 
 namespace {
@@ -773,11 +795,11 @@ extern "C" int attn_decode_flat(const void* q, int q_stride, const void* cache, 
 // and neither scratch nor counters is touched.  Otherwise `scratch`: attn_decode_scratch_floats(...) floats when
 // splits > 1, and `counters`: S * nkv ints, zero before the first launch (the kernel leaves them zero).  `inv_freq` (rot/2 floats) switches the fused rotation on: q is
 // then the unrotated projection row and, with store_kv, the new key and value are written here too.
-extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                           const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
-                           const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
-                           int num_pages, int window, float scale, int splits, int cluster_merge, int max_context,
-                           int* status, cudaStream_t stream) {
+extern "C" int attn_decode_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                  const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                                  const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                                  int num_pages, int window, int chunk, int sink, float scale, int splits, int cluster_merge,
+                                  int max_context, int* status, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (nq % nkv || nq / nkv > 16 || splits < 1) return (int)cudaErrorInvalidValue;
     if (splits == 1) cluster_merge = 0;
@@ -804,7 +826,7 @@ extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const
     CUtensorMap map;
     memset(&map, 0, sizeof map);
     int use_tma = 0;
-    if (DEC_TMA && g_decode_tma && window <= 0 && (page_size == 8 || page_size == 16 || page_size == 32)) {
+    if (DEC_TMA && g_decode_tma && window <= 0 && chunk <= 0 && (page_size == 8 || page_size == 16 || page_size == 32)) {
         static EncodeTiledFn fn = nullptr;
         if (!fn) {
             void* p = nullptr;
@@ -847,5 +869,15 @@ extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const
     cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta, group,
                                    cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
-                                   window, scale * LOG2E, num_pages, splits, cluster_merge, status);
+                                   window, chunk, sink, scale * LOG2E, num_pages, splits, cluster_merge, status);
+}
+
+extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                           const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                           const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                           int num_pages, int window, float scale, int splits, int cluster_merge, int max_context,
+                           int* status, cudaStream_t stream) {
+    return attn_decode_masked(q, q_stride, cache, meta, group, cu_tokens, positions, out, scratch, counters, inv_freq, rot,
+                              store_kv, S, nq, nkv, page_size, num_pages, window, 0, 0, scale, splits, cluster_merge, max_context,
+                              status, stream);
 }

@@ -406,18 +406,21 @@ extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const i
 // ----------------------------------------------------------------------------- attention over the cache
 // One block per (token, query head).  The query at position p reads the keys at
 // positions kstart..p of its request through the block table (kstart = 0, or
-// p - window + 1 for a windowed layer), 64 at a time in position order, with a
-// running maximum and sum (softmax in float32).  The order of every sum depends on
-// p and the window only, so the result is the same whether the token came alone,
-// in a portion of a prompt, or beside other requests.
+// p - window + 1 for a windowed layer, or the first position of p's chunk of `chunk`
+// positions for a layer that looks only inside chunks counted from position 0), 64 at a
+// time in position order, with a running maximum and sum (softmax in float32).  With
+// `sink` the softmax has one more term in its denominator, a key of score 0 that has no
+// value: the running maximum starts at 0 and the running sum at 1.  The order of every
+// sum depends on p, the window and the chunk only, so the result is the same whether the
+// token came alone, in a portion of a prompt, or beside other requests.
 #define ATTN_KT 64
 #define ATTN_THREADS 128
 template <typename T>
 __global__ void __launch_bounds__(ATTN_THREADS)
 attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ token_entry,
-                    const int* __restrict__ positions, T* __restrict__ out, int nq, int window, float scale,
-                    int num_pages, int* __restrict__ status) {
+                    const int* __restrict__ positions, T* __restrict__ out, int nq, int window, int chunk, int sink,
+                    float scale, int num_pages, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
@@ -434,9 +437,10 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
     const int ld = d + 1;
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
     for (int i = tid; i < d; i += ATTN_THREADS) qs[i] = to_float(qrow[i]);
-    float m = -INFINITY, l = 0.f;
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[2] = {0.f, 0.f};  // head sizes up to 2 * ATTN_THREADS
-    const int kstart = window > 0 ? max(0, p - window + 1) : 0;
+    int kstart = window > 0 ? max(0, p - window + 1) : 0;
+    if (chunk > 0) kstart = max(kstart, p - p % chunk);
     for (int k0 = kstart; k0 <= p; k0 += ATTN_KT) {
         const int n = min(ATTN_KT, p - k0 + 1);
         __syncthreads();  // the previous tile's values are no longer read
@@ -492,7 +496,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
 
 extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
                             const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
-                            int page_size, int num_pages, int window, float scale, int* status,
+                            int page_size, int num_pages, int window, int chunk, int sink, float scale, int* status,
                             cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d > 2 * ATTN_THREADS) return (int)cudaErrorInvalidValue;
@@ -509,8 +513,8 @@ extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int 
             configured_f32 = smem;
         }
         return (int)launch_kernel(attn_generic_kernel<float>, grid, ATTN_THREADS, smem, stream, (const float*)q, q_stride,
-                                  (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq, window, scale,
-                                  num_pages, status);
+                                  (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq, window, chunk, sink,
+                                  scale, num_pages, status);
     } else {
         if (smem > configured_bf16) {
             e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -519,7 +523,7 @@ extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int 
         }
         return (int)launch_kernel(attn_generic_kernel<__nv_bfloat16>, grid, ATTN_THREADS, smem, stream,
                                   (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry,
-                                  positions, (__nv_bfloat16*)out, nq, window, scale, num_pages, status);
+                                  positions, (__nv_bfloat16*)out, nq, window, chunk, sink, scale, num_pages, status);
     }
 }
 

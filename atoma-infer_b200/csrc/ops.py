@@ -24,7 +24,7 @@ MAX_GROUPS = 8
 STATUS_WORDS = 8
 SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the weights
 
-CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/linear_stream.cu", "kernels/sampling.cu"]
+CORE_SOURCES = ["kernels/core.cu", "kernels/layer_ops.cu", "kernels/linear_bf16.cu", "kernels/linear_stream.cu", "kernels/sampling.cu"]
 ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
 GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
@@ -86,6 +86,7 @@ class CudaOps:
         mode = os.environ.get("ATOMA_INFER_PDL", "linear+norm")
         self.pdl = {"0": 0, "1": 1, "linear": 2, "linear+norm": 6}.get(mode, 6)
         self.fused_rope = True  # the decode attention rotates q and k and writes the new key and value itself
+        self.masked_fast_attention = True  # chunk masks and sinks on the tensor-core attention kernels (False: on the plain one; a test lever)
         # Few-row linears go to the persistent, TMA-fed kernel (kernels/linear_stream.cu) where it is the faster one
         # (see _stream_linear); ATOMA_INFER_STREAM_LINEAR=0 keeps them all on the kernel that loads weights into
         # fragments directly (kernels/linear_bf16.cu).  The kernel tests set the attribute.
@@ -335,6 +336,67 @@ class CudaOps:
     def silu_mul(self, gu, out, meta, T: int, inter: int):
         self._check(self.lib.silu_mul(_p(gu), _p(out), _code(gu), _p(meta), T, inter, self._stream()), "silu_mul")
 
+    # ------------------------------------------------------------------ layers other than the plain pre-norm block
+    @staticmethod
+    def _slot_stride(state) -> ctypes.c_longlong:
+        """Floats from one slot's ring to the next (a part's state is a slice of the layer's per-request state)."""
+        if state is None:
+            return ctypes.c_longlong(0)
+        if state.dtype != torch.float32 or state.dim() != 3 or state[0].stride() != (state.shape[2], 1):
+            raise KernelError("a convolution state is float32 [slots, rows, channels] with contiguous rows")
+        return ctypes.c_longlong(state.stride(0))
+
+    def short_conv(self, x, w, state, ctx, out, *, add_input: bool = True):
+        """out[t] = (x[t] +) sum_j w[:, j] * x[t - taps + 1 + j] over the float32 residual rows of each request, zeros
+        before its start; rows before the step's portion come from ``state`` (float32 [slots, taps - 1, C], the row of
+        position p at place p mod (taps - 1); None when taps is 1).  ``short_conv_save`` writes the state afterwards."""
+        C, taps = w.shape
+        self._check(self.lib.short_conv(_p(x), _p(w), _p(state), _p(out), _code(out), _p(ctx.meta), _p(ctx.positions),
+                                        _p(ctx.token_entry), _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.T, C, taps,
+                                        int(add_input), self._slot_stride(state), self._stream()), "short_conv")
+
+    def short_conv_save(self, x, state, ctx, taps: int):
+        """The last taps - 1 rows of x of every entry go to its state (see ``short_conv``)."""
+        if taps > 1:
+            self._check(self.lib.short_conv_save(_p(x), _p(state), _p(ctx.meta), _p(ctx.positions), _p(ctx.token_entry),
+                                                 _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.T, x.shape[1], taps,
+                                                 self._slot_stride(state), self._stream()), "short_conv_save")
+
+    def scaled_add_rmsnorm(self, resid, delta, alpha: float, w, eps: float, ctx, *, keep=None, conv=None):
+        """The norm after the sum: resid <- rmsnorm(alpha * resid + delta) * w, in place, float32.
+        ``keep=(state, taps)``: the rows as they were before go to that convolution state (the last taps - 1 of every
+        entry).  ``conv=(w, state, out)``, decode steps only: also out <- new row + short convolution of it over
+        ``state``, the input of the sublayer that follows."""
+        H = resid.shape[1]
+        k_state, k_taps = keep if keep is not None else (None, 0)
+        c_w, c_state, c_out = conv if conv is not None else (None, None, None)
+        self._check(self.lib.scaled_add_rmsnorm(_p(resid), _p(delta), _code(delta) if delta is not None else DT_F32,
+                                                ctypes.c_float(alpha), _p(w), ctypes.c_float(eps), _p(ctx.meta), ctx.T, H,
+                                                _p(k_state), int(k_taps), self._slot_stride(k_state), self._slot_stride(c_state),
+                                                _p(ctx.positions), _p(ctx.token_entry),
+                                                _p(ctx.cu_tokens), _p(ctx.state_slots), _p(c_w), _p(c_state),
+                                                c_w.shape[1] if c_w is not None else 0, _p(c_out),
+                                                _code(c_out) if c_out is not None else DT_F32, self._stream()),
+                    "scaled_add_rmsnorm")
+
+    def qkv_prepare(self, qkv, ctx, cache_layer, group: int, q_out, *, nq: int, nkv: int, d: int, dv: int, dp: int,
+                    page_size: int, num_pages: int, store_kv: bool, bias=None, q_norm=None, k_norm=None, eps: float = 0.0,
+                    inv_freq=None, rot: int = 0, v_first=None, v_lambda=None, v_out=None):
+        """Rows [q | k | v] of the fused projection become attention's inputs: biases, root-mean-square norms over
+        the whole q and the whole k part (weights ``q_norm`` / ``k_norm``), rotation of the first ``rot`` dims of
+        every head, v <- (1 - lambda) v + lambda v_first; q to ``q_out`` [T, nq * dp], k and v to the pages as heads of
+        dp elements (zeros behind d and dv).  ``v_out``: the values (biases added, unmixed) for later layers."""
+        self._check(self.lib.qkv_prepare(_p(qkv), _code(qkv), _p(bias), _p(q_norm), _p(k_norm), ctypes.c_float(eps),
+                                         _p(ctx.positions), _p(ctx.token_entry), _p(ctx.meta), max(group, 0), _p(inv_freq),
+                                         int(rot) if inv_freq is not None else 0, _p(v_first), _p(v_lambda), _p(v_out),
+                                         _p(q_out), _p(cache_layer), ctx.T, nq, nkv, d, dv, dp, page_size, num_pages,
+                                         int(store_kv), _p(self.status), self._stream()), "qkv_prepare")
+
+    def polynorm(self, z, coef, eps: float, out, meta):
+        """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(u) = u / sqrt(mean(u^2) + eps); coef = (a, b, c, e)."""
+        self._check(self.lib.polynorm(_p(z), _code(z), _p(coef), ctypes.c_float(eps), _p(out), _p(meta), z.shape[0],
+                                      z.shape[1], self._stream()), "polynorm")
+
     def rope_kv_store(self, qkv, positions, token_entry, meta, group: int, inv_freq, cache_layer, num_pages: int,
                       T: int, nq: int, nkv: int, d: int, rot: int, page_size: int, store_kv: bool):
         self._check(self.lib.rope_kv_store(_p(qkv), _code(qkv), _p(positions), _p(token_entry), _p(meta), group,
@@ -347,21 +409,30 @@ class CudaOps:
                 and q_stride % 8 == 0)
 
     def attention(self, q, q_stride: int, cache_layer, ctx, group: int, out, nq: int, nkv: int, d: int,
-                  page_size: int, num_pages: int, window: int, scale: float, rope=None):
+                  page_size: int, num_pages: int, window: int, scale: float, rope=None, chunk: int = 0, sink: bool = False):
         """Attention of the step's queries over what their requests have cached (the step's own
         keys included).  bfloat16 with a head size in steps of 16 up to 256 runs the tensor-core
         kernels (one library per head size, built at first use); anything else, and all of
         float32, runs the plain kernel.  ``rope`` = (inv_freq, rotary_dim, store_kv): only for decode
         steps on the fast path (see ``fast_attention``); the queries are then still unrotated and the
-        kernel rotates them, and writes the new key and value, itself."""
+        kernel rotates them, and writes the new key and value, itself.  ``chunk`` > 0: a query sees only the keys of
+        its own chunk of that many positions (chunks counted from position 0 of the request).  ``sink``: the softmax
+        has one more term in its denominator, a key of score 0 without a value."""
         T, S = ctx.T, ctx.S
+        if (chunk or sink) and self.fast_attention(q.dtype, d, nq, nkv, q_stride) and not self.masked_fast_attention:
+            self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
+                                              _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
+                                              num_pages, window, int(chunk), int(bool(sink)), ctypes.c_float(scale),
+                                              _p(self.status), self._stream()), "attn_generic")
+            return
         if rope is not None and not (ctx.decode_only and self.fast_attention(q.dtype, d, nq, nkv, q_stride)):
             raise KernelError("fused rotation exists for decode steps on the bfloat16 fast path only")
         if self.fast_attention(q.dtype, d, nq, nkv, q_stride):
             lib = self._attention_library(d)
             if ctx.decode_only:
                 inv_freq, rot, store = rope if rope is not None else (None, 0, False)
-                flat_blocks = self._decode_flat_blocks(lib, d, S, nkv)
+                # a chunk bounds the keys of a request and a sink is one more partial result: both go with fixed splits
+                flat_blocks = 0 if (chunk or sink) else self._decode_flat_blocks(lib, d, S, nkv)
                 if flat_blocks:
                     # large batch: as many blocks as the GPU holds share all key tiles evenly
                     n = lib.attn_decode_flat_scratch_floats(S, nq, nkv, flat_blocks)
@@ -374,7 +445,8 @@ class CudaOps:
                                                      page_size, num_pages, window, ctypes.c_float(scale), flat_blocks,
                                                      _p(self.status), self._stream()), "attn_decode_flat")
                     return
-                splits = self.decode_splits(S, nkv, ctx.max_context, lib.attn_decode_blocks_per_sm())
+                seen = min(ctx.max_context, chunk) if chunk else ctx.max_context  # most keys a request reads
+                splits = self.decode_splits(S, nkv, seen, lib.attn_decode_blocks_per_sm())
                 # the splits merge inside a thread-block cluster when they fit one, else through scratch
                 if S <= SKINNY_MAX_ROWS:
                     self._prefetch_next_weight(S)
@@ -383,30 +455,31 @@ class CudaOps:
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
                 if not cluster and S * nkv > self._counters.numel():
                     raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
-                self._check(lib.attn_decode(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                            _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
-                                            rot, int(store), S, nq, nkv, page_size, num_pages,
-                                            window, ctypes.c_float(scale), splits, int(cluster), ctx.max_context,
-                                            _p(self.status), self._stream()),
+                self._check(lib.attn_decode_masked(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                   _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
+                                                   rot, int(store), S, nq, nkv, page_size, num_pages,
+                                                   window, int(chunk), int(bool(sink)), ctypes.c_float(scale), splits,
+                                                   int(cluster), ctx.max_context, _p(self.status), self._stream()),
                             "attn_decode")
-            elif self._prefill_tc(d, page_size, nq, nkv) is not None:
+            elif not (chunk or sink) and self._prefill_tc(d, page_size, nq, nkv) is not None:
                 tc = self._prefill_tc(d, page_size, nq, nkv)
                 self._check(tc.attn_prefill_tc(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                                _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
                                                page_size, num_pages, window, ctypes.c_float(scale), ctx.max_context,
                                                _p(self.status), self._stream()), "attn_prefill_tc")
             else:
-                self._check(lib.attn_prefill(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                             _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
-                                             page_size, num_pages, window, ctypes.c_float(scale), ctx.max_context,
-                                             _p(self.status), self._stream()), "attn_prefill")
+                self._check(lib.attn_prefill_masked(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                    _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                                    page_size, num_pages, window, int(chunk), int(bool(sink)),
+                                                    ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
+                            "attn_prefill")
             return
         if d > 256:
             raise KernelError(f"head size {d} is not supported (at most 256)")
         self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
                                           _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
-                                          num_pages, window, ctypes.c_float(scale), _p(self.status), self._stream()),
-                    "attn_generic")
+                                          num_pages, window, int(chunk), int(bool(sink)), ctypes.c_float(scale),
+                                          _p(self.status), self._stream()), "attn_generic")
 
     # ------------------------------------------------------------------ whole layers of a decode step
     def _decode_stack_library(self, d: int):

@@ -12,7 +12,20 @@ misses that case (models/src/flash_attention.rs:384-410).
 
 Parameters: ``hidden``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``,
 ``window`` (None: all keys), ``position`` (spec of the position encoding).
-Checkpoint tensors: ``<prefix>.{q,k,v,o}_proj.weight``.
+Checkpoint tensors: ``<prefix>.{q,k,v,o}_proj.weight`` (other suffixes: ``names``).
+
+Further options, all off by default:
+``chunk``: a query sees only keys of its own chunk of that many positions, counted from position 0;
+``sink``: one more term in the softmax's denominator, a key of score 0 without a value;
+``v_head_dim``: values of another size than queries and keys;
+``bias``: q, k and v projections have biases;
+``qk_norm`` ``{"eps": e}``: the whole q projection, and the whole k projection, is divided by its root mean square
+and multiplied by a weight of its size, before the rotation;
+``v_mix`` ``{"key": name}``: the first layer with this key leaves its values for the step, every later one caches
+(1 - lambda) v + lambda v_first with its own learned scalar lambda.
+With any of the last four the rows are prepared by one kernel (``qkv_prepare``) that writes queries, keys and values
+as heads of one padded size, the next multiple of 16 above both sizes, which the tensor-core kernels read like any
+other head size; the output projection's matrix gets zero columns to match.
 """
 from __future__ import annotations
 
@@ -38,6 +51,17 @@ class Attention(Mixer):
         self.window = p.get("window")
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.v_head_dim = int(p.get("v_head_dim") or self.head_dim)
+        self.chunk = int(p.get("chunk") or 0)
+        self.sink = bool(p.get("sink", False))
+        self.bias = bool(p.get("bias", False))
+        self.qk_norm = p.get("qk_norm")
+        self.v_mix = p.get("v_mix")
+        self.prepared = bool(self.bias or self.qk_norm is not None or self.v_mix is not None or self.v_head_dim != self.head_dim)
+        self.padded_dim = -(-max(self.head_dim, self.v_head_dim) // 16) * 16 if self.prepared else self.head_dim
+        self.names = {"q": ".q_proj.weight", "k": ".k_proj.weight", "v": ".v_proj.weight", "o": ".o_proj.weight",
+                      "q_bias": ".q_proj.bias", "k_bias": ".k_proj.bias", "v_bias": ".v_proj.bias",
+                      "q_norm": ".q_norm.weight", "k_norm": ".k_norm.weight", "v_mix": ".v_mix", **(p.get("names") or {})}
         pos = dict(p.get("position") or {"kind": "none"})
         pos.setdefault("head_dim", self.head_dim)
         self.position = part_class("position", pos["kind"])(pos, prefix)
@@ -50,47 +74,98 @@ class Attention(Mixer):
     def kv_size(self):
         return self.num_kv_heads * self.head_dim
 
+    @property
+    def v_size(self):
+        return self.num_kv_heads * self.v_head_dim
+
     def activation_width(self):
-        return self.q_size + 2 * self.kv_size
+        return max(self.q_size + self.kv_size + self.v_size, 2 * self.num_heads * self.padded_dim)
 
     def streamed_weights(self):
         return [self.w_qkv, self.w_o]
 
     def cache_need(self):
-        return CacheNeed.kv(self.num_kv_heads, self.head_dim, self.window)
+        return CacheNeed.kv(self.num_kv_heads, self.padded_dim, self.window)
 
     def declare(self):
-        pre = self.prefix
-        return [
-            TensorDecl(pre + ".q_proj.weight", (self.q_size, self.hidden)),
-            TensorDecl(pre + ".k_proj.weight", (self.kv_size, self.hidden)),
-            TensorDecl(pre + ".v_proj.weight", (self.kv_size, self.hidden)),
-            TensorDecl(pre + ".o_proj.weight", (self.hidden, self.q_size)),
-        ] + self.position.declare()
+        pre, n = self.prefix, self.names
+        decls = [
+            TensorDecl(pre + n["q"], (self.q_size, self.hidden)),
+            TensorDecl(pre + n["k"], (self.kv_size, self.hidden)),
+            TensorDecl(pre + n["v"], (self.v_size, self.hidden)),
+            TensorDecl(pre + n["o"], (self.hidden, self.num_heads * self.v_head_dim)),
+        ]
+        if self.bias:
+            decls += [TensorDecl(pre + n["q_bias"], (self.q_size,)), TensorDecl(pre + n["k_bias"], (self.kv_size,)),
+                      TensorDecl(pre + n["v_bias"], (self.v_size,))]
+        if self.qk_norm is not None:
+            decls += [TensorDecl(pre + n["q_norm"], (self.q_size,), init="ones"),
+                      TensorDecl(pre + n["k_norm"], (self.kv_size,), init="ones")]
+        if self.v_mix is not None:
+            decls.append(TensorDecl(pre + n["v_mix"], ()))
+        return decls + self.position.declare()
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        pre = self.prefix
+        pre, n = self.prefix, self.names
         # One matrix [q; k; v]: each output element is the same dot product as before.
-        self.w_qkv = torch.cat([tensors[pre + ".q_proj.weight"], tensors[pre + ".k_proj.weight"],
-                                tensors[pre + ".v_proj.weight"]], dim=0).contiguous()
-        self.w_o = tensors[pre + ".o_proj.weight"].contiguous()
+        self.w_qkv = torch.cat([tensors[pre + n["q"]], tensors[pre + n["k"]], tensors[pre + n["v"]]], dim=0).contiguous()
+        self.w_o = tensors[pre + n["o"]].contiguous()
         self.position.bind(tensors, rt)
+        if not self.prepared:
+            return
+        f32 = lambda name: tensors[pre + n[name]].to(torch.float32).contiguous()  # noqa: E731  (exact widening)
+        self.b_qkv = torch.cat([f32("q_bias"), f32("k_bias"), f32("v_bias")]).contiguous() if self.bias else None
+        self.w_q_norm, self.w_k_norm = (f32("q_norm"), f32("k_norm")) if self.qk_norm is not None else (None, None)
+        self.v_lambda = f32("v_mix").reshape(1) if self.v_mix is not None else None
+        if self.padded_dim != self.v_head_dim:  # the attention's output has heads of the padded size: zero columns for the tail
+            w = self.w_o.new_zeros((self.hidden, self.num_heads, self.padded_dim))
+            w[:, :, :self.v_head_dim] = self.w_o.view(self.hidden, self.num_heads, self.v_head_dim)
+            self.w_o = w.view(self.hidden, self.num_heads * self.padded_dim).contiguous()
 
     def fused(self):
         rotary = self.position.rotary()
-        if rotary is None:
+        if rotary is None or self.prepared or self.chunk or self.sink:
             return None
         return {"kind": "attention", "w_qkv": self.w_qkv, "w_o": self.w_o, "hidden": self.hidden,
                 "num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
                 "scale": self.scale, "window": int(self.window or 0), "inv_freq": rotary[0], "rotary_dim": rotary[1]}
 
+    def _forward_prepared(self, x, ctx, cache):
+        ops = self.rt.ops
+        H, G, dp = self.num_heads, self.num_kv_heads, self.padded_dim
+        qkv = ops.linear(x, self.w_qkv, meta=ctx.meta)
+        q = torch.empty((ctx.T, H * dp), dtype=x.dtype, device=x.device)
+        v_first = v_out = None
+        if self.v_mix is not None:
+            key = "v_mix:" + str(self.v_mix.get("key", ""))
+            v_first = ctx.shared.get(key)
+            if v_first is None:  # the first such layer of the step: its values are what later layers mix in
+                v_out = ctx.shared[key] = torch.empty((ctx.T, self.v_size), dtype=x.dtype, device=x.device)
+            elif tuple(v_first.shape) != (ctx.T, self.v_size):
+                raise ValueError(f"{self.prefix}: mixes values of {v_first.shape[1]} elements a token into {self.v_size}")
+        rotary = self.position.rotary()
+        ops.qkv_prepare(qkv, ctx, cache.pages, cache.group, q, nq=H, nkv=G, d=self.head_dim, dv=self.v_head_dim, dp=dp,
+                        page_size=cache.page_size, num_pages=cache.num_pages,
+                        store_kv=cache.writes and cache.pages is not None, bias=self.b_qkv, q_norm=self.w_q_norm,
+                        k_norm=self.w_k_norm, eps=float((self.qk_norm or {}).get("eps", 0.0)),
+                        inv_freq=rotary[0] if rotary else None, rot=rotary[1] if rotary else 0, v_first=v_first,
+                        v_lambda=self.v_lambda if v_first is not None else None, v_out=v_out)
+        out = torch.empty((ctx.T, H * dp), dtype=x.dtype, device=x.device)
+        ops.attention(q, H * dp, cache.pages, ctx, cache.group, out, H, G, dp, cache.page_size, cache.num_pages,
+                      int(self.window or 0), self.scale, chunk=self.chunk, sink=self.sink)
+        return ops.linear(out, self.w_o, meta=ctx.meta)
+
     def forward(self, x, ctx, cache):
+        if self.prepared:
+            return self._forward_prepared(x, ctx, cache)
         ops = self.rt.ops
         qkv = ops.linear(x, self.w_qkv, meta=ctx.meta)
         # In a decode step the attention kernel can rotate q and write the new key and value itself.
         rope = None
         fast = getattr(ops, "fast_attention", None)
+        if self.chunk or self.sink:
+            fast = None  # the fused rotation is the plain decode kernel's
         if ctx.decode_only and getattr(ops, "fused_rope", True) and fast and fast(qkv.dtype, self.head_dim, self.num_heads, self.num_kv_heads, qkv.shape[1]):
             rotary = self.position.rotary()
             if rotary is not None:
@@ -100,7 +175,8 @@ class Attention(Mixer):
                                            head_dim=self.head_dim)
         out = torch.empty((ctx.T, self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(qkv, qkv.shape[1], cache.pages, ctx, cache.group, out, self.num_heads, self.num_kv_heads,
-                      self.head_dim, cache.page_size, cache.num_pages, int(self.window or 0), self.scale, rope=rope)
+                      self.head_dim, cache.page_size, cache.num_pages, int(self.window or 0), self.scale, rope=rope,
+                      **({"chunk": self.chunk, "sink": self.sink} if self.chunk or self.sink else {}))
         return ops.linear(out, self.w_o, meta=ctx.meta)
 
 

@@ -69,6 +69,9 @@ class StepContext:
     page_size: int = 0
     table_offsets: Sequence[int] = ()   # per cache group: where its block tables start in ``meta`` ...
     table_strides: Sequence[int] = ()   # ... and how long a request's row is
+    # What one layer leaves for later layers of the same step (an earlier layer's values that later ones mix in,
+    # for instance), by a name the parts agree on.  Lives as long as the step.
+    shared: Dict[str, Any] = field(default_factory=dict)
 
     def block_table(self, group: int) -> torch.Tensor:
         """The block tables of a cache group as a device view [S, pages per request]: entry k's row lists its
@@ -146,6 +149,23 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class SequenceFilter(Part):
+    """What a sublayer reads instead of the residual rows themselves: a function of a request's rows over time that
+    needs only a fixed number of earlier rows, which it keeps as state (a short causal convolution, for instance)."""
+
+    def state_bytes(self) -> int:
+        return 0
+
+    def forward(self, resid: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor]) -> torch.Tensor:
+        """``resid`` float32 [T, H]; ``state`` the part's share of the per-request state, uint8 [slots, state_bytes];
+        returns the sublayer's input in the compute dtype.  Reads the state, does not write it."""
+        raise NotImplementedError
+
+    def save(self, resid: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor]) -> None:
+        """The step's rows of ``resid`` (what ``forward`` was given) enter the state; called after ``forward``."""
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
     """How positions enter a mixer.  For attention: ``encode_and_store`` turns the fused
     q|k|v rows of a step into position-encoded queries (in place) and writes keys and
@@ -192,8 +212,13 @@ class Block(Part):
     mixer: Mixer
 
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
-                cache: LayerCache) -> torch.Tensor:
+                cache: LayerCache) -> Optional[torch.Tensor]:
         raise NotImplementedError
+
+    def state_bytes(self) -> int:
+        """Bytes of fixed-size state per request that the block's parts keep together (the mixer's, by default);
+        a block with more stateful parts hands each its share of ``cache.state``."""
+        return self.mixer.state_bytes()
 
     def decode_fusion(self) -> Optional[Dict[str, Any]]:
         """For a kernel that runs a run of whole layers of a decode step: this block's arrangement and what its

@@ -1,13 +1,22 @@
-"""Pre-norm residual block: h = x + mixer(norm1(x)); out = h + ff(norm2(h))
-(models/src/llama.rs:393-410).  The residual stream is float32 and each addition
-happens inside the norm that follows it.
+"""Residual blocks.
 
-Parameters: ``norm`` (spec of both norms), ``mixer``, ``feed_forward`` (specs), and
-the names of the four parts inside the layer's prefix (``names``).
+Pre-norm: h = x + mixer(norm1(x)); out = h + ff(norm2(h)) (models/src/llama.rs:393-410).  The residual stream
+is float32 and each addition happens inside the norm that follows it.  Parameters: ``norm`` (spec of both norms),
+``mixer``, ``feed_forward`` (specs), and the names of the four parts inside the layer's prefix (``names``).
+
+Post-norm: x <- norm1(alpha x + mixer(f1(x))); x <- norm2(alpha x + ff(f2(x))): the norm comes after the sum and
+what it leaves IS the residual stream (float32); the sublayers read the stream itself, optionally through a
+sequence filter (f1, f2: a short convolution over time, whose state the block keeps per request).  Parameters:
+``norm``, ``mixer``, ``feed_forward`` (None: the layer has no second sublayer), ``alpha``, ``filter`` (spec or
+None), ``names``.
 """
 from __future__ import annotations
 
 from ..config.registry import part_class, register_part
+from typing import Optional
+
+import torch
+
 from .base import Block
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
@@ -56,3 +65,94 @@ class PreNormBlock(Block):
 
 
 register_part("block", "prenorm", PreNormBlock)
+
+
+_POST_NAMES = {"norm1": "norm1", "mixer": "mix", "norm2": "norm2", "feed_forward": "mlp", "filter1": "canon1",
+               "filter2": "canon2"}
+
+
+class PostNormBlock(Block):
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        names = {**_POST_NAMES, **(params.get("names") or {})}
+        mk = lambda fam, spec, name: part_class(fam, spec["kind"])(spec, f"{prefix}.{name}")  # noqa: E731
+        self.alpha = float(params.get("alpha", 1.0))
+        self.norm1 = mk("norm", params["norm"], names["norm1"])
+        self.mixer = mk("mixer", params["mixer"], names["mixer"])
+        ff, flt = params.get("feed_forward"), params.get("filter")
+        self.feed_forward = mk("feed_forward", ff, names["feed_forward"]) if ff else None
+        self.norm2 = mk("norm", params["norm"], names["norm2"]) if ff else None
+        self.filter1 = mk("filter", flt, names["filter1"]) if flt else None
+        self.filter2 = mk("filter", flt, names["filter2"]) if flt and ff else None
+
+    def parts(self):
+        return [p for p in (self.filter1, self.mixer, self.norm1, self.filter2, self.feed_forward, self.norm2) if p is not None]
+
+    def streamed_weights(self):
+        return self.mixer.streamed_weights() + (self.feed_forward.streamed_weights() if self.feed_forward else [])
+
+    def activation_width(self):
+        return max(p.activation_width() for p in self.parts())
+
+    def declare(self):
+        return [d for p in self.parts() for d in p.declare()]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        for p in self.parts():
+            p.bind(tensors, rt)
+
+    def _layout(self):
+        """Shares of the per-request state: the mixer's, then the two filters', each starting on 16 bytes."""
+        shares, at = {}, 0
+        for name in ("mixer", "filter1", "filter2"):
+            part = getattr(self, name)
+            n = part.state_bytes() if part is not None else 0
+            shares[name] = (at, n)
+            at += -(-n // 16) * 16
+        return shares, at
+
+    def state_bytes(self):
+        return self._layout()[1]
+
+    def _share(self, state: Optional[torch.Tensor], name: str) -> Optional[torch.Tensor]:
+        at, n = self._layout()[0][name]
+        return state[:, at:at + n] if state is not None and n else None
+
+    def forward(self, resid, delta, ctx, cache):
+        if delta is not None:  # a block before this one left its addition pending
+            resid.add_(delta)
+        ops = self.rt.ops
+        mixer_cache = cache
+        if self.mixer.state_bytes() != self.state_bytes() and cache.state is not None:
+            from dataclasses import replace
+            mixer_cache = replace(cache, state=self._share(cache.state, "mixer"))
+        s1, s2 = self._share(cache.state, "filter1"), self._share(cache.state, "filter2")
+        # decode steps: the norm kernel also leaves the next sublayer's input (new row + its short convolution)
+        f2 = self.filter2.fused() if self.filter2 is not None else None
+        fuse = (ctx.decode_only and ctx.T == ctx.S and f2 is not None and f2["kind"] == "short_conv" and f2["add_input"]
+                and getattr(ops, "fused_post_norm", True))
+        h = self.filter1.forward(resid, ctx, s1) if self.filter1 is not None else self._plain_input(resid)
+        a = self.mixer.forward(h, ctx, mixer_cache)
+        keep1 = (self.filter1.ring(s1), self.filter1.taps) if self.filter1 is not None else None
+        h2 = None
+        if self.feed_forward is not None and fuse:
+            h2 = torch.empty((ctx.T, resid.shape[1]), dtype=self.rt.dtype, device=resid.device)
+            self.norm1.forward_post(resid, a, self.alpha, ctx, keep=keep1,
+                                    conv=(f2["weight"], self.filter2.ring(s2), h2))
+        else:
+            self.norm1.forward_post(resid, a, self.alpha, ctx, keep=keep1)
+        if self.feed_forward is None:
+            return None
+        if h2 is None:
+            h2 = self.filter2.forward(resid, ctx, s2) if self.filter2 is not None else self._plain_input(resid)
+        f = self.feed_forward.forward(h2, ctx)
+        keep2 = (self.filter2.ring(s2), self.filter2.taps) if self.filter2 is not None else None
+        self.norm2.forward_post(resid, f, self.alpha, ctx, keep=keep2)
+        return None
+
+    def _plain_input(self, resid):
+        return resid if resid.dtype == self.rt.dtype else resid.to(self.rt.dtype)
+
+
+register_part("block", "postnorm", PostNormBlock)

@@ -50,3 +50,45 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class PolyNormFF(FeedForward):
+    """Dense feed-forward with a polynomial activation of normalised powers: down(act(up(x))),
+    act(z) = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(u) = u / sqrt(mean(u^2) + eps) over
+    the row's ``intermediate`` values, taken in float32.
+
+    Parameters: ``hidden``, ``intermediate``, ``eps``, ``names`` (suffixes of up, down and the four coefficients;
+    default ``.up``, ``.down``, ``.act``).
+    """
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.eps = float(params["eps"])
+        names = {"up": ".up", "down": ".down", "coef": ".act", **(params.get("names") or {})}
+        self.t_up, self.t_down, self.t_coef = (prefix + names[k] for k in ("up", "down", "coef"))
+
+    def activation_width(self):
+        return self.intermediate
+
+    def declare(self):
+        return [TensorDecl(self.t_up, (self.intermediate, self.hidden)), TensorDecl(self.t_down, (self.hidden, self.intermediate)),
+                TensorDecl(self.t_coef, (4,))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_up, self.w_down = tensors[self.t_up].contiguous(), tensors[self.t_down].contiguous()
+        self.coef = tensors[self.t_coef].to(torch.float32).contiguous()
+
+    def streamed_weights(self):
+        return [self.w_up, self.w_down]
+
+    def forward(self, x, ctx):
+        ops = self.rt.ops
+        z = ops.linear(x, self.w_up, meta=ctx.meta)
+        act = torch.empty_like(z)
+        ops.polynorm(z, self.coef, self.eps, act, ctx.meta)
+        return ops.linear(act, self.w_down, meta=ctx.meta)
+
+
+register_part("feed_forward", "polynorm", PolyNormFF)

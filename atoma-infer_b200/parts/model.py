@@ -22,7 +22,7 @@ from .base import LayerCache, Runtime, StepContext
 from .decode_stack import MAX_ROWS as STACK_MAX_ROWS, plan_stacks
 
 # the registrations of the built-in parts
-from . import attention, block, embedding, feed_forward, head, norm, position  # noqa: F401
+from . import attention, block, embedding, feed_forward, filter, head, norm, position  # noqa: F401
 
 
 @dataclass
@@ -130,7 +130,7 @@ class DecoderModel:
             self.run_group[i] = (gi, len(self.groups[gi].layers))
             self.groups[gi].layers.append(i)
         # fixed-size state per request, for every run of a mixer that has some
-        self.state_bytes = [self.blocks[r.layer].mixer.state_bytes() for r in self.runs]
+        self.state_bytes = [self.blocks[r.layer].state_bytes() for r in self.runs]
         # a step of this model can be captured in a CUDA graph if no part reads the host-side entry list
         self.graph_safe = all(getattr(p, "graph_safe", False)
                               for p in [self.embedding, self.head] + [blk.mixer for blk in self.blocks])

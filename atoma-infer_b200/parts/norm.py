@@ -2,7 +2,12 @@
 
 The reference uses candle's RmsNorm for input_layernorm, post_attention_layernorm
 and model.norm (models/src/llama.rs:402, 408, 416-421, 474, 487).  Parameters:
-``size`` and ``eps`` (config.json's rms_norm_eps).  Checkpoint tensor: ``<prefix>.weight``.
+``size`` and ``eps`` (config.json's rms_norm_eps); ``weight_offset`` (default 0): the
+stored weight is w - offset, i.e. 1.0 for weights kept around zero; ``tensor_suffix``
+(default ".weight"): the checkpoint tensor is ``<prefix><suffix>``.
+
+``forward_post`` is the norm AFTER the sum: resid <- norm(alpha * resid + delta), the
+normed rows being the new residual stream (float32, in place).
 """
 from __future__ import annotations
 
@@ -18,13 +23,19 @@ class RMSNorm(Norm):
         super().__init__(params, prefix)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.offset = float(params.get("weight_offset", 0.0))
+        self.tensor = self.prefix + str(params.get("tensor_suffix", ".weight"))
 
     def declare(self):
-        return [TensorDecl(self.prefix + ".weight", (self.size,), init="ones")]
+        return [TensorDecl(self.tensor, (self.size,), init="jitter" if self.offset == 1.0 else "ones")]
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.weight = tensors[self.prefix + ".weight"].to(torch.float32).contiguous()  # exact widening
+        self.weight = (tensors[self.tensor].to(torch.float32) + self.offset).contiguous()  # widened exactly, then the offset
+
+    def forward_post(self, resid, delta, alpha, ctx, keep=None, conv=None):
+        """resid <- rmsnorm(alpha * resid + delta) * weight.  ``keep`` / ``conv``: see ``scaled_add_rmsnorm``."""
+        self.rt.ops.scaled_add_rmsnorm(resid, delta, alpha, self.weight, self.eps, ctx, keep=keep, conv=conv)
 
     def forward(self, resid, delta, ctx, rows=None, num_rows=0):
         n = num_rows if rows is not None else ctx.T

@@ -8,7 +8,9 @@ and sin are computed in float32 inside the kernel that also writes keys and valu
 to their pages, so no table exists.  Pairs are (x[i], x[i + rot/2]) (:250).
 
 Parameters: ``head_dim``, ``theta``, ``scaling`` (dict or None), ``rotary_dim``
-(defaults to head_dim).  ``kind: "none"`` is the same kernel with zero frequencies.
+(defaults to head_dim), ``exact_frequencies`` (default False: float32 arithmetic as
+above; True: theta^(-2i/rot) taken in float64 and rounded once to float32).
+``kind: "none"`` is the same kernel with zero frequencies.
 """
 from __future__ import annotations
 
@@ -47,6 +49,11 @@ class RotaryEncoding(PositionEncoding):
         self.scaling = params.get("scaling")
 
     def _frequencies(self):
+        if self.params.get("exact_frequencies"):
+            if self.scaling:
+                raise ValueError("exact_frequencies goes with unscaled frequencies only")
+            idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
+            return torch.pow(torch.tensor(self.theta, dtype=torch.float64), -idx / self.rotary_dim).to(torch.float32)
         return rotary_inv_freq(self.head_dim, self.theta, self.scaling, self.rotary_dim)
 
     def bind(self, tensors, rt):

@@ -44,8 +44,8 @@ class WeightError(ValueError):
 class TensorDecl:
     """One checkpoint tensor a part needs.
 
-    init: 'normal' (N(0, std)), 'ones' (1 + N(0, jitter)), 'zeros', or 'index'
-    (an integer table filled with arange modulo ``index_mod``).
+    init: 'normal' (N(0, std)), 'ones' (1 + N(0, jitter)), 'zeros', 'jitter' (N(0, jitter)),
+    or 'index' (an integer table filled with arange modulo ``index_mod``).
     """
 
     name: str

@@ -44,8 +44,10 @@ def random_tensor(decl: TensorDecl, seed: int, *, std: float, norm_jitter: float
         t = torch.ones(decl.shape, dtype=torch.float32, device=device)
         if norm_jitter:
             t = t + torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * norm_jitter
-    elif decl.init == "zeros":
+    elif decl.init in ("zeros", "jitter"):  # jitter: N(0, norm_jitter), a norm weight that is stored around zero
         t = torch.zeros(decl.shape, dtype=torch.float32, device=device)
+        if decl.init == "jitter" and norm_jitter:
+            t = t + torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * norm_jitter
     else:
         raise ValueError(f"unknown init {decl.init!r} for {decl.name}")
     return t.to(dtype)
@@ -69,13 +71,10 @@ def write_random_model(model_dir: str, config: dict, seed: int, *, std: float = 
                        norm_jitter: float = 0.0, dtype: torch.dtype = torch.bfloat16,
                        scales: Optional[Mapping[str, float]] = None, device="cpu") -> str:
     """Writes ``config.json`` and ``model.safetensors`` for the architecture ``config`` names."""
-    from ..config.registry import architecture
+    from ..config.registry import architecture, architecture_name
     from ..parts.model import declared_tensors
 
-    archs = config.get("architectures")
-    if not archs:
-        raise ValueError("the configuration needs an 'architectures' list to choose the model")
-    arch = architecture(archs[0])
+    arch = architecture(architecture_name(config))
     spec = arch.build_spec(arch.parse_config(config))
     decls = declared_tensors(spec)
     os.makedirs(model_dir, exist_ok=True)

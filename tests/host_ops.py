@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import torch
 
+import plain_dosovik as PD
 import plain_llama as P
 from atoma_infer_b200.csrc.ops import (META_BT_OFFSET, META_BT_STRIDE, META_NUM_ROWS, META_NUM_TOKENS, STATUS_WORDS,
                                        CudaOps)
@@ -93,7 +94,80 @@ class HostOps:
                 cache[page, 0, :, p % page_size] = qk[t, nq:].to(cache.dtype)
                 cache[page, 1, :, p % page_size] = rows[t, nq + nkv:].to(cache.dtype)
 
-    def attention(self, q, q_stride, cache, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale, rope=None):
+    # -- layers other than the plain pre-norm block (rings: the row of position p at place p mod (taps - 1))
+    def _entries(self, ctx):
+        n, S = int(ctx.meta[META_NUM_TOKENS]), int(ctx.meta[1])
+        cu = [int(ctx.cu_tokens[k]) for k in range(S)] + [n]
+        return [(k, cu[k], cu[k + 1], int(ctx.state_slots[k])) for k in range(S)]
+
+    def short_conv(self, x, w, state, ctx, out, *, add_input=True):
+        self._count()
+        taps = w.shape[1]
+        for _, a, b, slot in self._entries(ctx):
+            p0 = int(ctx.positions[a])
+            past = [state[slot, p % (taps - 1)] if p >= 0 else torch.zeros_like(x[0]) for p in range(p0 - taps + 1, p0)]
+            rows = torch.stack(past + list(x[a:b])) if past else x[a:b]
+            y = PD.short_conv(rows.float(), w.float())[len(past):]
+            out[a:b] = ((x[a:b] + y) if add_input else y).to(out.dtype)
+
+    def short_conv_save(self, x, state, ctx, taps):
+        self._count()
+        for _, a, b, slot in self._entries(ctx):
+            for t in range(max(a, b - (taps - 1)), b):
+                state[slot, int(ctx.positions[t]) % (taps - 1)] = x[t]
+
+    def scaled_add_rmsnorm(self, resid, delta, alpha, w, eps, ctx, *, keep=None, conv=None):
+        n = int(ctx.meta[META_NUM_TOKENS])
+        if keep is not None and keep[0] is not None:
+            self.short_conv_save(resid, keep[0], ctx, keep[1])
+        self._count()
+        v = alpha * resid[:n] + (delta[:n].float() if delta is not None else 0)
+        resid[:n] = PD.rms_divide(v, eps) * w
+        if conv is not None:
+            self.short_conv(resid, conv[0], conv[1], ctx, conv[2], add_input=True)
+
+    def qkv_prepare(self, qkv, ctx, cache, group, q_out, *, nq, nkv, d, dv, dp, page_size, num_pages, store_kv, bias=None,
+                    q_norm=None, k_norm=None, eps=0.0, inv_freq=None, rot=0, v_first=None, v_lambda=None, v_out=None):
+        self._count()
+        meta = ctx.meta
+        n = int(meta[META_NUM_TOKENS])
+        off, stride = int(meta[META_BT_OFFSET + group]), int(meta[META_BT_STRIDE + group])
+        NQ, NK = nq * d, nkv * d
+        rows = qkv[:n].float() + (bias if bias is not None else 0)
+        q, k, v = rows[:, :NQ], rows[:, NQ:NQ + NK], rows[:, NQ + NK:]
+        if q_norm is not None:
+            q = PD.rms_divide(q, eps) * q_norm
+        if k_norm is not None:
+            k = PD.rms_divide(k, eps) * k_norm
+        q, k = q.reshape(n, nq, d).clone(), k.reshape(n, nkv, d).clone()
+        if inv_freq is not None and rot:
+            pos = ctx.positions[:n]
+            q[..., :rot] = P.rope(q[..., :rot], pos, inv_freq)
+            k[..., :rot] = P.rope(k[..., :rot], pos, inv_freq)
+        if v_out is not None:
+            v_out[:n] = v.to(v_out.dtype)
+        if v_first is not None:
+            v = (1 - v_lambda) * v + v_lambda * v_first[:n].float()
+        q_out[:n] = 0
+        q_out[:n].view(n, nq, dp)[..., :d] = q.to(q_out.dtype)
+        if store_kv:
+            for t in range(n):
+                p = int(ctx.positions[t])
+                page = int(meta[off + int(ctx.token_entry[t]) * stride + p // page_size])
+                if not 0 < page < num_pages:
+                    self.status[1] = t + 1
+                    continue
+                cache[page, :, :, p % page_size] = 0
+                cache[page, 0, :, p % page_size, :d] = k[t].to(cache.dtype)
+                cache[page, 1, :, p % page_size, :dv] = v[t].reshape(nkv, dv).to(cache.dtype)
+
+    def polynorm(self, z, coef, eps, out, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        out[:n] = PD.poly_norm(z[:n].float(), coef, eps).to(out.dtype)
+
+    def attention(self, q, q_stride, cache, ctx, group, out, nq, nkv, d, page_size, num_pages, window, scale, rope=None,
+                  chunk=0, sink=False):
         self._count()
         meta = ctx.meta
         n = int(meta[META_NUM_TOKENS])
@@ -101,6 +175,8 @@ class HostOps:
         for t in range(n):
             pos, e = int(ctx.positions[t]), int(ctx.token_entry[t])
             first = max(0, pos - window + 1) if window else 0
+            if chunk:
+                first = max(first, pos - pos % chunk)
             idx = range(first, pos + 1)
             pages = [int(meta[off + e * stride + j // page_size]) for j in idx]
             k = torch.stack([cache[p, 0, :, j % page_size] for p, j in zip(pages, idx)]).float()  # [keys, nkv, d]
@@ -108,7 +184,8 @@ class HostOps:
             qq = q[t].view(-1, d)[:nq].float()
             g = nq // nkv
             for h in range(nq):
-                w = torch.softmax((k[:, h // g] @ qq[h]) * scale, 0)
+                sc = (k[:, h // g] @ qq[h]) * scale
+                w = torch.softmax(torch.cat([sc, sc.new_zeros(1)]), 0)[:-1] if sink else torch.softmax(sc, 0)
                 out[t, h * d:(h + 1) * d] = (w @ v[:, h // g]).to(out.dtype)
 
     def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None, slots=None):

@@ -1,0 +1,94 @@
+"""Dosovik on the GPU through the replay program and the engine: every cutting of the work against the plain
+implementation, in both number formats, for configurations that differ in every size and option."""
+import pytest
+import torch
+
+import dosovik_helpers as DH
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOP1 = 0.9
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for i, name in enumerate(DH.CONFIGS):
+        d = str(tmp_path_factory.mktemp("dosovik" + name))
+        DH.make_model(d, name, seed=20 + i)
+        out[name] = (d,) + DH.CONFIGS[name]
+    return out
+
+
+# lengths around the chunk sizes (21, 40, 64 and 96, none) and the pages' edges
+LENGTHS = {"P": (1, 2, 20, 22, 43, 90, 131), "Q": (3, 39, 41, 81, 160), "R": (5, 63, 65, 130, 200), "S": (1, 17, 70)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(DH.CONFIGS))
+def test_every_cutting_matches_plain(name, dtype, models, tmp_path):
+    d, cfg, page = models[name]
+    seqs = helpers.random_tokens(cfg["vocab"], LENGTHS[name], seed=3)
+    ref = DH.plain_logits(d, cfg, seqs)
+    families = {
+        "w": helpers.trace_whole(seqs, tag="w"),
+        "t": helpers.trace_tail(seqs, tail=48, tag="t"),           # decoding passes chunk edges
+        "c": helpers.trace_chunks(seqs, tag="c"),                  # portions of 1 to 11 tokens
+        "m": helpers.trace_mixed(seqs, tag="m"),
+    }
+    steps = [s for f in families.values() for s in f]
+    longest = sorted((len(v) for v in seqs.values()), reverse=True)[:4]
+    max_tokens = sum(-(-n // 64) * 64 for n in longest)             # pages and slots are used again
+    steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), max_tokens, page)
+    tol = helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL
+    for tag in families:
+        sub = [s for s in steps if s["entries"][0]["id"].startswith(tag)]
+        worst, where, agree, clear = helpers.compare_trace(sub, out, cfg["vocab"], ref)
+        assert worst <= tol, f"family {tag!r}: error {worst:.3g} of the logit scale at (step, request, position) {where}"
+        if dtype == "float32":
+            assert agree == 1.0, f"family {tag!r}: greedy tokens differ from the plain implementation"
+        else:
+            assert agree >= BF16_TOP1 and clear == 1.0, f"family {tag!r}: top-1 agreement {agree:.3f} ({clear:.3f} where clear)"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_one_token_at_a_time(dtype, models, tmp_path):
+    """A short prompt, then hundreds of single-token steps through the captured decode graph: several chunks,
+    many pages, the convolution's ring turned over a hundred times."""
+    d, cfg, page = models["P"]
+    seq = helpers.random_tokens(cfg["vocab"], (330,), seed=11)
+    ref = DH.plain_logits(d, cfg, seq)
+    steps = helpers.trace_tail(seq, tail=322)
+    steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 384, page)
+    worst, where, agree, clear = helpers.compare_trace(steps, out, cfg["vocab"], ref)
+    assert worst <= (helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL), (worst, where)
+    assert agree == 1.0 if dtype == "float32" else agree > 0.95
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_through_the_engine(dtype, models):
+    """Greedy tokens through the entry point and the scheduler, with few pages and a small token budget (prompts in
+    portions, preemption and recomputation, slots used again), against the plain loop."""
+    from atoma_infer_b200.engine import Engine
+    from atoma_infer_b200.sampling import SamplingParams
+
+    d, cfg, page = models["R"]
+    prompts = list(helpers.random_tokens(cfg["vocab"], (3, 70, 9, 130, 21), seed=8).values())
+    eng = Engine(d, dtype=dtype, block_size=page, num_gpu_blocks_override=40, max_num_sequences=3, max_num_batched_tokens=48)
+    outs = eng.generate(prompts, SamplingParams(do_sample=False, max_new_tokens=12, ignore_eos_token=True))
+    eng.lm.rt.ops.check_status()
+    assert eng.lm.manager.audit() == "" and eng.lm.manager.num_requests() == 0
+    w = helpers.read_weights(d)
+    import plain_dosovik as PD
+
+    for p, o in zip(prompts, outs):
+        got = o.token_ids
+        if dtype == "float32":
+            assert got == DH.plain_greedy(d, cfg, p, 12)
+            continue
+        logits = PD.forward(cfg, w, list(p) + list(got))  # each token judged on the engine's own history
+        for i, tok in enumerate(got):
+            row = logits[len(p) - 1 + i]
+            lead = float(row.max() - row[tok]) / float(row.abs().max())
+            assert lead <= 2 * helpers.BF16_TOL, (i, tok, lead)
