@@ -15,7 +15,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 
 from ..csrc.build import host_library
-from .spec import FULL_KEYS, WINDOW_KEYS, CacheGroup, CacheNeed
+from .spec import CHUNK_KEYS, FULL_KEYS, WINDOW_KEYS, CacheGroup, CacheNeed
 
 _ERRORS = {
     -20: "an entry brings no tokens", -21: "a request appears twice in one step",
@@ -101,7 +101,7 @@ class CacheManager:
         n = len(self.groups)
         arr = ctypes.c_int * max(n, 1)
         kinds = arr(*[g.need.kind for g in self.groups])
-        windows = arr(*[(g.need.window or 0) for g in self.groups])
+        windows = arr(*[g.need.span for g in self.groups])
         pages = arr(*[g.num_pages for g in self.groups])
         self._h = self._lib.cm_create(page_size, n, kinds, windows, pages, max_seqs)
         if not self._h:

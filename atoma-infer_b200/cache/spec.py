@@ -6,7 +6,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-FULL_KEYS, WINDOW_KEYS = 0, 1
+FULL_KEYS, WINDOW_KEYS, CHUNK_KEYS = 0, 1, 2
 
 
 @dataclass(frozen=True)
@@ -24,18 +24,28 @@ class CacheNeed:
     values of attention are the instance ``CacheNeed.kv(num_kv_heads, head_dim)``; a mixer that caches one
     latent vector, or keys and values of different widths, names its own.  ``window`` = how many cached tokens
     a query looks back over (itself included), None for all of them; pages a window has passed go back to
-    the pool."""
+    the pool.  ``chunk`` = a query looks only at the cached tokens of its own chunk of that many positions
+    (chunks counted from position 0); pages that lie wholly before the newest position's chunk go back to the pool.
+    With both, the window decides what is given back (it never starts after what a query still needs)."""
 
     tensors: Tuple[CachedTensor, ...]
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     @staticmethod
-    def kv(num_kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheNeed":
-        return CacheNeed((CachedTensor("k", num_kv_heads, head_dim), CachedTensor("v", num_kv_heads, head_dim)), window)
+    def kv(num_kv_heads: int, head_dim: int, window: Optional[int] = None, chunk: Optional[int] = None) -> "CacheNeed":
+        return CacheNeed((CachedTensor("k", num_kv_heads, head_dim), CachedTensor("v", num_kv_heads, head_dim)), window, chunk)
 
     @property
     def kind(self) -> int:
-        return FULL_KEYS if self.window is None else WINDOW_KEYS
+        if self.window is not None:
+            return WINDOW_KEYS
+        return FULL_KEYS if self.chunk is None else CHUNK_KEYS
+
+    @property
+    def span(self) -> int:
+        """The window or the chunk size, whichever the kind goes by (0: all keys)."""
+        return int(self.window or self.chunk or 0)
 
     @property
     def elements_per_token(self) -> int:

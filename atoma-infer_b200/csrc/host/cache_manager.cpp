@@ -36,8 +36,10 @@ int CacheManager::add_request(int64_t req) {
 
 // First absolute page index that a request of `num_tokens` cached tokens still
 // needs: its next query sits at position num_tokens and looks back over `window`
-// keys, itself included, so the oldest key needed is num_tokens - window + 1.
+// keys, itself included, so the oldest key needed is num_tokens - window + 1.  With chunks
+// the oldest key needed is the first position of that query's chunk.
 int64_t CacheManager::first_needed_page(const Group& g, int64_t num_tokens) const {
+    if (g.spec.kind == kChunkKeys) return (num_tokens - num_tokens % (int64_t)g.spec.window) / page_size_;
     if (g.spec.kind != kWindowKeys) return 0;
     int64_t oldest = num_tokens - (int64_t)g.spec.window + 1;
     if (oldest <= 0) return 0;

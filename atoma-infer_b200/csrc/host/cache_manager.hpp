@@ -20,7 +20,8 @@
 
 namespace engine {
 
-enum CacheKind : int { kFullKeys = 0, kWindowKeys = 1 };
+// kChunkKeys: a query sees only the keys of its own chunk of `window` positions, chunks counted from position 0
+enum CacheKind : int { kFullKeys = 0, kWindowKeys = 1, kChunkKeys = 2 };
 
 enum CacheStatus : int {
     kOk = 0,
@@ -35,7 +36,7 @@ enum CacheStatus : int {
 
 struct GroupSpec {
     int kind;       // CacheKind
-    int window;     // keys a query may look back over, itself included (kWindowKeys only)
+    int window;     // kWindowKeys: keys a query may look back over, itself included; kChunkKeys: positions of a chunk
     int num_pages;  // pool size including the reserved page 0
 };
 

@@ -21,7 +21,7 @@ void* cm_create(int page_size, int num_groups, const int* kinds, const int* wind
     std::vector<GroupSpec> groups;
     for (int g = 0; g < num_groups; ++g) {
         if (num_pages[g] < 1) return nullptr;
-        if (kinds[g] == engine::kWindowKeys && windows[g] <= 0) return nullptr;
+        if ((kinds[g] == engine::kWindowKeys || kinds[g] == engine::kChunkKeys) && windows[g] <= 0) return nullptr;
         groups.push_back(GroupSpec{kinds[g], windows[g], num_pages[g]});
     }
     return new (std::nothrow) CacheManager(page_size, groups, max_seqs);

@@ -180,11 +180,14 @@ __device__ __forceinline__ uint32_t swz(int row, int c) { return (uint32_t)row *
 
 }  // namespace
 
+// CS: the instantiation that knows chunk masks and the softmax's sink (the plain one keeps its registers)
+template <bool CS>
 __global__ void __launch_bounds__(TC_THREADS, HEAD_DIM == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, int q_stride,
                        CacheLayout L, const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
-                       const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, float scale_log2,
-                       int num_pages, int bt_cap, int* __restrict__ status) {
+                       const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, int chunk_arg, int sink_arg,
+                       float scale_log2, int num_pages, int bt_cap, int* __restrict__ status) {
+    const int chunk = CS ? chunk_arg : 0, sink = CS ? sink_arg : 0;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int STAGE = HALVES * HALF_BYTES;  // one K or V tile: 128 rows of the head
@@ -214,7 +217,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     const int nt = min(TPT, q_len - t0);
     const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)e * meta[META_BT_STRIDE + group];
     const int p_first = ctx + t0, p_last = p_first + nt - 1;
-    const int kbeg = window > 0 ? max(0, p_first - window + 1) : 0, kend = p_last + 1;
+    // chunk > 0: a row sees only the keys of its own chunk of positions; the first row's chunk starts earliest
+    int kbeg = window > 0 ? max(0, p_first - window + 1) : 0;
+    if (chunk > 0) kbeg = max(kbeg, p_first - p_first % chunk);
+    const int kend = p_last + 1;
+    const int chunk_last = chunk > 0 ? p_last - p_last % chunk : 0;  // keys before it are hidden from some row
     const int k_first = (kbeg / BKV) * BKV;
     const int ntiles = (kend - k_first + BKV - 1) / BKV;
     const int page_lo = k_first / ps;
@@ -358,7 +365,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         constexpr int DH = D / 2;  // my half of the head
         // m_run: the row's maximum so far; m_base: the base of the exponentials, which follows it lazily;
         // l_run: the sum over my half of the keys, in units of 2^m_base (the halves add up at the end)
-        float m_run = -INFINITY, m_base = -INFINITY, l_run = 0.f;
+        // sink: one more key of score 0 without a value; maximum and base start there, and one of the row's two
+        // threads starts its sum with the sink's term
+        float m_run = sink ? 0.f : -INFINITY, m_base = m_run, l_run = sink && half == 0 ? 1.f : 0.f;
+        // the first key my row sees: its window's or its chunk's start
+        int my_lo = window > 0 ? my_pos - window + 1 : 0;
+        if (chunk > 0 && my_pos >= 0) my_lo = max(my_lo, my_pos - my_pos % chunk);
         bool ok = true;
 
         // After a timeout anywhere in the block every wait returns at once and `ok` stays false, but the
@@ -376,12 +388,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);
-            const bool need_mask = window > 0 || k0 + BKV - 1 > p_first || k0 < kbeg || nt < TPT;  // same for the whole block
+            const bool need_mask = window > 0 || k0 + BKV - 1 > p_first || k0 < kbeg || nt < TPT || k0 < chunk_last;  // same for the whole block
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     int key = k0 + half * 64 + i;
-                    bool vis = key <= my_pos && (window <= 0 || my_pos - key < window);
+                    bool vis = CS ? (key <= my_pos && key >= my_lo) : (key <= my_pos && (window <= 0 || my_pos - key < window));
                     v[i] = vis ? v[i] : -INFINITY;
                 }
             }
@@ -513,10 +525,10 @@ extern "C" int attn_prefill_tc_supports(int page_size, int nq, int nkv) {
     return ps_ok && nq % nkv == 0 && nq / nkv <= 16;
 }
 
-extern "C" int attn_prefill_tc(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                               const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
-                               int page_size, int num_pages, int window, float scale, int max_context, int* status,
-                               cudaStream_t stream) {
+extern "C" int attn_prefill_tc_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                      const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
+                                      int nkv, int page_size, int num_pages, int window, int chunk, int sink, float scale,
+                                      int max_context, int* status, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
     if (!attn_prefill_tc_supports(page_size, nq, nkv)) return (int)cudaErrorInvalidValue;
     EncodeTiledFn fn = encode_fn();
@@ -534,17 +546,34 @@ extern "C" int attn_prefill_tc(const void* q, int q_stride, const void* cache, c
     CacheLayout L{nkv, page_size, D};
     const int tpt = BQ / (nq / nkv);
     int span = window > 0 ? min(max_context, window + tpt + 2 * BKV) : max_context;
+    if (chunk > 0) span = min(span, chunk + tpt + 2 * BKV);
     int bt_cap = span / page_size + 2 + BKV / page_size;
     size_t smem = TC_SMEM_FIXED + (size_t)bt_cap * sizeof(int);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t err = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool cs = chunk > 0 || sink;
+    static size_t configured[2] = {0, 0};
+    if (smem > configured[cs]) {
+        cudaError_t err = cs ? cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                             : cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
-        configured = smem;
+        configured[cs] = smem;
     }
     dim3 grid(nkv, (max_q_len + tpt - 1) / tpt, S);
-    attn_prefill_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens, ctx_lens,
-                                                        (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
+    if (cs)
+        attn_prefill_tc_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens,
+                                                                  ctx_lens, (bf16*)out, nq, window, chunk, sink, scale * LOG2E,
+                                                                  num_pages, bt_cap, status);
+    else
+        attn_prefill_tc_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens,
+                                                                   ctx_lens, (bf16*)out, nq, window, 0, 0, scale * LOG2E,
+                                                                   num_pages, bt_cap, status);
     LAUNCH_RETURN();
+}
+
+extern "C" int attn_prefill_tc(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                               const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                               int page_size, int num_pages, int window, float scale, int max_context, int* status,
+                               cudaStream_t stream) {
+    return attn_prefill_tc_masked(q, q_stride, cache, meta, group, cu_tokens, ctx_lens, out, S, max_q_len, nq, nkv, page_size,
+                                  num_pages, window, 0, 0, scale, max_context, status, stream);
 }

@@ -85,7 +85,7 @@ class Attention(Mixer):
         return [self.w_qkv, self.w_o]
 
     def cache_need(self):
-        return CacheNeed.kv(self.num_kv_heads, self.padded_dim, self.window)
+        return CacheNeed.kv(self.num_kv_heads, self.padded_dim, self.window, self.chunk or None)
 
     def declare(self):
         pre, n = self.prefix, self.names

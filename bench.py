@@ -9,6 +9,9 @@ step's inputs copied from pinned host memory and the sampled tokens read back ev
 step.  Also: prefill of 2,048 tokens, decode at batch 1 and 64, and the decode step's
 fraction of the measured HBM bandwidth.  Prints ONE JSON line.
 
+``--designs`` instead of the benchmark: prefill and decode throughput of the Dosovik design beside Llama at equal
+layer sizes, and the design's own kernels beside Llama's like kernels with their fractions of the copy bandwidth.
+
 Tables for profiles/ instead of the JSON line: ``--linears [--model 1b|3b|8b]`` (the two few-row linear
 kernels on the four matrices of a layer) and ``--layer-kernel-phases`` (the persistent layer kernel's time
 per phase); ``--model 3b|8b`` alone runs that configuration's serving workload through ``Engine.generate``.
@@ -223,6 +226,166 @@ def few_row_linears(which: str) -> int:
     return 0
 
 
+# Layer sizes that resemble real models, used for both designs: (width, feed-forward, heads, key/value heads, head size)
+DESIGN_SIZES = {"w2048-h64": (2048, 8192, 32, 8, 64), "w3072-h128": (3072, 8192, 24, 8, 128), "w4096-h128": (4096, 14336, 32, 8, 128)}
+
+
+def design_configs(size: str, layers: int, vocab: int = 32768, chunk: int = 1024, value_dim: int = 0):
+    """(Llama config, Dosovik config) of equal width, heads, head size, feed-forward size, layers and vocabulary."""
+    import math
+
+    H, I, nq, nkv, d = DESIGN_SIZES[size]
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": H, "intermediate_size": I, "vocab_size": vocab,
+             "num_hidden_layers": layers, "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d,
+             "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072, "tie_word_embeddings": False}
+    mixer = {"heads": nq, "kv_heads": nkv, "dim": d, "vdim": value_dim or d, "scale": 1 / math.sqrt(d), "v_mix": True,
+             "mask": {"size": chunk}, "rot": {"dims": d // 2, "base": 500000.0}}
+    dosovik = {"architecture": "Dosovik", "vocab": vocab, "width": H, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+               "embedding": {"scale": math.sqrt(H)}, "canon": {"taps": 4},
+               "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": I}} for _ in range(layers)]}
+    return llama, dosovik
+
+
+def design_comparison(args) -> int:
+    """Prefill (one prompt of 2,048 tokens) and decode (8 requests, 2,048 tokens cached each, captured graphs)
+    through the step function for both designs at each size; then single kernels.  Timing: CUDA events, the median
+    of five regions after three warm-up runs; weights and activations of a step exceed the L2 at every size."""
+    import torch
+
+    import atoma_infer_b200  # noqa: F401
+    from atoma_infer_b200.engine import StepEntry
+    from atoma_infer_b200.engine.runtime import load_model, make_runtime
+
+    hbm, tflops, kind = peaks()
+    g = torch.Generator().manual_seed(5)
+    layers, batch, ctx_len, prefill = args.layers if args.layers != MODEL["num_hidden_layers"] else 8, args.batch, 2048, PREFILL_TOKENS
+
+    def median_ms(fn, n=5):
+        out = []
+        for i in range(3 + n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                out.append(a.elapsed_time(b))
+        return statistics.median(out)
+
+    rows = []
+    for size in DESIGN_SIZES:
+        for name, cfg in zip(("llama", "dosovik"), design_configs(size, layers)):
+            with tempfile.TemporaryDirectory() as d:
+                with open(os.path.join(d, "config.json"), "w") as f:
+                    json.dump(cfg, f)
+                pages = (batch + 1) * (-(-(ctx_len + 512) // PAGE)) + 64
+                lm = load_model(d, dtype="bfloat16", page_size=PAGE, num_pages=pages, max_seqs=batch + 1, cuda_graphs=True,
+                                random_weights_seed=1, max_batched_tokens=prefill)
+            vocab = lm.model.spec.vocab_size
+            toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()  # noqa: E731
+            before = lm.rt.ops.launches
+            nid = [0]
+
+            def one_prefill():
+                nid[0] += 1
+                lm.step.run([StepEntry(1000 + nid[0], toks(prefill), [prefill - 1])])
+                lm.step.finish(1000 + nid[0])
+            pre_ms = median_ms(one_prefill)
+            for r in range(batch):
+                lm.step.run([StepEntry(r, toks(ctx_len), [])])
+            cur = [toks(1) for _ in range(batch)]
+            steps = 16
+
+            def decode_steps():
+                for _ in range(steps):
+                    lm.step.run([StepEntry(r, cur[r], [0]) for r in range(batch)])
+            dec_ms = median_ms(decode_steps) / steps
+            lm.rt.ops.check_status()
+            weights = sum(w.numel() * w.element_size() for r in lm.model.runs for w in lm.model.blocks[r.layer].streamed_weights())
+            weights += lm.model.head.weight.numel() * 2
+            row = {"size": size, "design": name, "layers": layers, "prefill_tokens": prefill, "prefill_ms": round(pre_ms, 3),
+                   "prefill_tok_s": round(prefill / pre_ms * 1e3), "decode_batch": batch, "context": ctx_len,
+                   "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3),
+                   "decode_weight_bytes_over_copy_bandwidth": round(weights / (dec_ms * 1e-3) / (hbm * 1e9), 3),
+                   "launches": lm.rt.ops.launches - before}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+            del lm
+            torch.cuda.empty_cache()
+    design_kernels(make_runtime("bfloat16", "cuda:0"), hbm, median_ms)
+    return 0
+
+
+def design_kernels(rt, hbm, median_ms) -> None:
+    """The Dosovik layers' own kernels beside Llama's like kernels, alone, at width 2048 / 32 heads of 64 / 8 key heads /
+    feed-forward 8192: microseconds a call and the fraction of the copy bandwidth that the bytes each must move give.
+    Rows of 8,192 tokens (inputs and outputs beyond the L2) and of 8 tokens (a decode step; launch-bound)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kernel_utils as K
+
+    ops, dev = rt.ops, rt.device
+    H, I, nq, nkv, d, taps = 2048, 8192, 32, 8, 64, 4
+    bf = torch.bfloat16
+    print(f"kernels alone (copy bandwidth {hbm:.0f} GB/s): name, rows, us, bytes moved / time / copy bandwidth")
+    for T in (8192, 8):
+        entries = [(0, T)] if T > 64 else [(100 + i, 1) for i in range(T)]
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 0)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        resid, delta = torch.randn(T, H, device=dev), torch.randn(T, H, device=dev).to(bf)
+        w = torch.ones(H, device=dev)
+        cw, state = torch.randn(H, taps, device=dev), torch.zeros(max(len(entries), 1), taps - 1, H, device=dev)
+        out = torch.empty(T, H, device=dev, dtype=bf)
+        qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(bf)
+        cache = torch.zeros(num_pages, 2, nkv, PAGE, d, device=dev, dtype=bf)
+        q_out = torch.empty(T, nq * d, device=dev, dtype=bf)
+        bias, qn, kn = (torch.ones(n, device=dev) for n in ((nq + 2 * nkv) * d, nq * d, nkv * d))
+        inv_freq = torch.ones(d // 2, device=dev)
+        v_first, lam = torch.randn(T, nkv * d, device=dev).to(bf), torch.tensor([0.3], device=dev)
+        z, gu = torch.randn(T, I, device=dev).to(bf), torch.randn(T, 2 * I, device=dev).to(bf)
+        act, coef = torch.empty(T, I, device=dev, dtype=bf), torch.tensor([0.5, 0.2, 0.1, 0.0], device=dev)
+        cases = [
+            ("dosovik: short convolution", lambda: ops.short_conv(resid, cw, state, ctx, out), T * H * (4 + 2)),
+            ("dosovik: norm after the sum (+ state rows)", lambda: ops.scaled_add_rmsnorm(resid, delta, 1.0, w, 1e-5, ctx, keep=(state, taps)), T * H * (4 + 2 + 4)),
+            ("llama:   add + RMSNorm", lambda: ops.add_rmsnorm(resid, delta, w, 1e-5, out, ctx.meta, T), T * H * (4 + 2 + 4 + 2)),
+            ("dosovik: attention rows (bias, norms, rotation, mix, pages)",
+             lambda: ops.qkv_prepare(qkv, ctx, cache, 0, q_out, nq=nq, nkv=nkv, d=d, dv=d, dp=d, page_size=PAGE, num_pages=num_pages,
+                                     store_kv=True, bias=bias, q_norm=qn, k_norm=kn, eps=1e-5, inv_freq=inv_freq, rot=d // 2,
+                                     v_first=v_first, v_lambda=lam), T * ((nq + 2 * nkv) * d * 2 * 2 + nkv * d * 2)),
+            ("llama:   rotation + pages", lambda: ops.rope_kv_store(qkv, ctx.positions, ctx.token_entry, ctx.meta, 0, inv_freq, cache, num_pages,
+                                                                    T, nq, nkv, d, d, PAGE, True), T * (nq + 2 * nkv) * d * 2 * 2),
+            ("dosovik: polynomial activation", lambda: ops.polynorm(z, coef, 1e-5, act, ctx.meta), T * I * 2 * 2),
+            ("llama:   SiLU * up", lambda: ops.silu_mul(gu, act, ctx.meta, T, I), T * I * 2 * 3),
+        ]
+        if T <= 64:
+            h2 = torch.empty(T, H, device=dev, dtype=bf)
+            cases.insert(2, ("dosovik: norm after the sum + next input (decode)",
+                             lambda: ops.scaled_add_rmsnorm(resid, delta, 1.0, w, 1e-5, ctx, keep=(state, taps), conv=(cw, state, h2)),
+                             T * H * (4 + 2 + 4 + 2)))
+        for name, fn, nbytes in cases:
+            def many():
+                for _ in range(20):
+                    fn()
+            us = median_ms(many) / 20 * 1e3
+            print(f"  {name:62s} {T:5d} rows {us:8.1f} us  {nbytes / (us * 1e-6) / (hbm * 1e9):5.2f}")
+        # attention: a prompt of T tokens (or T decode tokens over 2,048 cached ones), plain and with chunk mask + sink
+        entries = [(0, T)] if T > 64 else [(2047, 1)] * T
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 1)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        cache = torch.randn(num_pages, 2, nkv, PAGE, d, device=dev).to(bf)
+        q, o = torch.randn(T, nq * d, device=dev).to(bf), torch.empty(T, nq * d, device=dev, dtype=bf)
+        for name, kw in (("llama:   attention", {}), ("dosovik: attention, chunks of 1024 + sink", {"chunk": 1024, "sink": True}),
+                         ("dosovik: attention, sink alone", {"sink": True})):
+            def many():
+                for _ in range(10):
+                    ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, 0, 0.125, **kw)
+            us = median_ms(many) / 10 * 1e3
+            print(f"  {name:62s} {T:5d} rows {us:8.1f} us")
+    ops.check_status()
+
+
 def layer_kernel_phases(eng, args, prompt, greedy, cfg) -> int:
     """Decode steps through the persistent layer kernel (csrc/kernels/decode_stack.cu), eagerly, with every block
     writing the global clock after each phase and each barrier of each layer; prints the mean, the slowest and the
@@ -327,6 +490,9 @@ def main() -> int:
     ap.add_argument("--linears", action="store_true",
                     help="instead of the benchmark: the four linears of a layer (sizes of --model) at 1, 8 and 16 rows on the "
                          "direct and on the streamed few-row kernel, weights cold (a table, for profiles/)")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the benchmark: prefill and decode throughput of the Dosovik design beside Llama at equal "
+                         "layer sizes (a JSON line each), then the design's kernels alone beside Llama's like kernels")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="measure only one phase (for profiling); the JSON line then lacks the other")
     args = ap.parse_args()
@@ -343,6 +509,8 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.linears:
         return few_row_linears(args.model)
+    if args.designs:
+        return design_comparison(args)
     if args.model != "1b":
         return serving_workload(args.model)
 

@@ -136,3 +136,31 @@ def test_random_orders_of_requests_keep_the_books(seed):
     for r in list(live):
         m.free_request(r)
     assert m.num_free_pages() == 24 and m.num_free_slots() == 5 and m.audit() == ""
+
+
+def test_pages_before_the_newest_chunk_go_back():
+    """Chunks of 10 positions, pages of 4: a query at position p needs keys from p - p % 10 on, so once a request
+    holds 10 tokens pages 0 and 1 are free again (page 2 holds positions 8..11), at 20 tokens pages 2, 3 and 4."""
+    groups = [CacheGroup(CacheNeed.kv(2, 16, chunk=10), [0], 9)]
+    m = CacheManager(4, groups, 2)
+    m.add_request(1)
+    m.reserve(1, 9)
+    m.advance(1, 9)
+    assert m.table(1) == [8, 7, 6] and m.num_free_pages() == 5
+    m.reserve(1, 10)
+    assert m.advance(1, 1) == 2                      # ten tokens held: the next query opens the second chunk
+    assert m.table(1) == [-1, -1, 6] and m.num_free_pages() == 7
+    # a portion that crosses into the third chunk: its first rows still look at the second, nothing goes before the step ends
+    m.reserve(1, 23)
+    assert [p >= 0 for p in m.table(1)] == [False, False, True, True, True, True]
+    assert m.advance(1, 13) == 3
+    assert [p >= 0 for p in m.table(1)] == [False] * 5 + [True]
+    assert m.audit() == ""
+    # a long request fits a pool that could never hold all its tokens
+    m.add_request(2)
+    for upto in range(1, 200, 7):
+        m.reserve(2, upto)
+        m.advance(2, upto - m.num_tokens(2))
+    assert m.audit() == ""
+    m.free_request(1), m.free_request(2)
+    assert m.num_free_pages() == m.num_usable_pages() and m.audit() == ""
