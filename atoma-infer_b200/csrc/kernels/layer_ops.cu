@@ -17,13 +17,35 @@ __global__ void __launch_bounds__(256)
 short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ state,
                   TO* __restrict__ y, const int* __restrict__ meta, const int* __restrict__ positions,
                   const int* __restrict__ token_entry, const int* __restrict__ cu_tokens,
-                  const int* __restrict__ slots, int C, int taps, int add_input, long long slot_stride) {
+                  const int* __restrict__ slots, int C, int taps, int add_input, long long slot_stride, int vec4) {
+    pdl_wait();  // like the norm kernel: the kernels behind start once this one's wait is over
     pdl_launch_dependents();
-    pdl_wait();
     const int t = blockIdx.x;
     if (t >= meta[META_NUM_TOKENS]) return;
     const int e = token_entry[t], p = positions[t], first = cu_tokens[e], R = taps - 1;
     const float* st = state + (size_t)slots[e] * slot_stride;
+    if (vec4) {  // four channels a thread, 16-byte accesses (C a multiple of 4, buffers on 16 bytes)
+        for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+            const float* wc = w + (size_t)c * taps;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < taps; ++j) {  // oldest tap first: a fixed order
+                const int back = taps - 1 - j, src = p - back;
+                if (src < 0) continue;
+                float v[4];
+                load4((t - back >= first) ? x + (size_t)(t - back) * C + c : st + (size_t)(src % R) * C + c, v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i] = fmaf(wc[i * taps + j], v[i], acc[i]);
+            }
+            if (add_input) {
+                float v[4];
+                load4(x + (size_t)t * C + c, v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i] += v[i];
+            }
+            store4(y + (size_t)t * C + c, acc);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         const float* wc = w + (size_t)c * taps;
         float acc = 0.f;
@@ -43,11 +65,12 @@ extern "C" int short_conv(const float* x, const float* w, const float* state, vo
                           int C, int taps, int add_input, long long slot_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = C >= 1024 ? 256 : 128;
+    const int vec4 = C % 4 == 0 && slot_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)state | (uintptr_t)y) & 15) == 0;
     if (y_dtype == DT_F32)
-        return (int)launch_kernel(short_conv_kernel<float>, T, threads, 0, stream, x, w, state, (float*)y, meta, positions,
-                                  token_entry, cu_tokens, slots, C, taps, add_input, slot_stride);
-    return (int)launch_kernel(short_conv_kernel<__nv_bfloat16>, T, threads, 0, stream, x, w, state, (__nv_bfloat16*)y, meta,
-                              positions, token_entry, cu_tokens, slots, C, taps, add_input, slot_stride);
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, short_conv_kernel<float>, T, threads, 0, stream, x, w, state, (float*)y, meta, positions,
+                                  token_entry, cu_tokens, slots, C, taps, add_input, slot_stride, vec4);
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, short_conv_kernel<__nv_bfloat16>, T, threads, 0, stream, x, w, state, (__nv_bfloat16*)y, meta,
+                              positions, token_entry, cu_tokens, slots, C, taps, add_input, slot_stride, vec4);
 }
 
 // Whether row t is one of the last R rows of its entry, i.e. one the state keeps.
@@ -93,9 +116,9 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
                           const int* __restrict__ positions, const int* __restrict__ token_entry,
                           const int* __restrict__ cu_tokens, const int* __restrict__ slots,
                           const float* __restrict__ conv_w, const float* __restrict__ conv_state, int conv_taps,
-                          TO* __restrict__ conv_out) {
+                          TO* __restrict__ conv_out, int vec4) {
     __shared__ float red[33];
-    extern __shared__ float row[];  // H floats
+    extern __shared__ __align__(16) float row[];  // H floats
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -107,18 +130,44 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
     if (keep && keeps_row(t, e, cu_tokens, keep_rows))
         kept = keep + (size_t)slots[e] * keep_stride + (size_t)(positions[t] % keep_rows) * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float old = x[i];
-        if (kept) kept[i] = old;
-        const float v = dl ? fmaf(alpha, old, to_float(dl[i])) : alpha * old;
-        row[i] = v;
-        ss = fmaf(v, v, ss);
+    if (vec4) {  // four values a thread, 16-byte accesses; the sum's order differs from the scalar form's, but is as fixed
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float old[4], d[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+            load4(x + i, old);
+            if (kept) store4(kept + i, old);
+            if (dl) load4(dl + i, d);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                v[k] = dl ? fmaf(alpha, old[k], d[k]) : alpha * old[k];
+                ss = fmaf(v[k], v[k], ss);
+            }
+            store4(row + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float old = x[i];
+            if (kept) kept[i] = old;
+            const float v = dl ? fmaf(alpha, old, to_float(dl[i])) : alpha * old;
+            row[i] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)H + eps);
     const int R = conv_taps - 1;
     const int p = conv_out ? positions[t] : 0;
     const float* st = conv_out ? conv_state + (size_t)slots[e] * conv_stride : nullptr;
+    if (vec4 && !conv_out) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float v[4], wv[4];
+            load4(row + i, v);
+            load4(w + i, wv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = v[k] * inv * wv[k];
+            store4(x + i, v);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const float v = row[i] * inv * w[i];
         x[i] = v;
@@ -145,10 +194,11 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
     const int threads = H >= 1024 ? 256 : 128;
     const size_t smem = (size_t)H * sizeof(float);
     if (keep_taps <= 1) keep = nullptr;
+    const int vec4 = H % 4 == 0 && keep_stride % 4 == 0 && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)keep) & 15) == 0;
 #define POSTNORM_CASE(TD, TO) \
     return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, scaled_add_rmsnorm_kernel<TD, TO>, n, threads, smem, stream, resid, \
                                   (const TD*)delta, alpha, w, eps, meta, H, keep, keep_taps - 1, keep_stride, conv_stride, positions, token_entry, \
-                                  cu_tokens, slots, conv_w, conv_state, conv_taps, (TO*)conv_out)
+                                  cu_tokens, slots, conv_w, conv_state, conv_taps, (TO*)conv_out, vec4)
     if (delta_dtype == DT_F32 && conv_out_dtype == DT_F32) POSTNORM_CASE(float, float);
     else if (delta_dtype == DT_F32) POSTNORM_CASE(float, __nv_bfloat16);
     else if (conv_out_dtype == DT_F32) POSTNORM_CASE(__nv_bfloat16, float);
@@ -174,20 +224,34 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias, co
                    const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
                    const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
                    T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
-                   int store_kv, int* __restrict__ status) {
-    extern __shared__ float vals[];  // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
+                   int store_kv, int vec4, int* __restrict__ status) {
+    extern __shared__ __align__(16) float vals[];  // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
     __shared__ float red[33];
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     if (t >= meta[META_NUM_TOKENS]) return;
     const int NQ = nq * d, NK = nkv * d, NV = nkv * dv;
     const T* row = qkv + (size_t)t * (NQ + NK + NV);
     float sq = 0.f, sk = 0.f;
-    for (int i = threadIdx.x; i < NQ + NK; i += blockDim.x) {
-        const float v = to_float(row[i]) + (bias ? bias[i] : 0.f);
-        vals[i] = v;
-        if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+    if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
+        for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
+            float v[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
+            load4(row + i, v);
+            if (bias) load4(bias + i, bv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                v[k] += bv[k];
+                if (i < NQ) sq = fmaf(v[k], v[k], sq); else sk = fmaf(v[k], v[k], sk);
+            }
+            store4(vals + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < NQ + NK; i += blockDim.x) {
+            const float v = to_float(row[i]) + (bias ? bias[i] : 0.f);
+            vals[i] = v;
+            if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+        }
     }
     float inv_q = 1.f, inv_k = 1.f;
     if (q_norm) inv_q = rsqrtf(block_sum(sq, red) / (float)NQ + eps);
@@ -209,6 +273,61 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias, co
     const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
     T* kpage = cache + (size_t)page * 2 * kv_block + (size_t)slot * dp;
     T* vpage = kpage + kv_block;
+    const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
+    if (vec4) {
+        // q and k: one item per (head, four dims); an item of the rotated part's first half also makes its partner
+        const int upd = dp / 4, heads = nq + (page > 0 ? nkv : 0);
+        for (int it = threadIdx.x; it < heads * upd; it += blockDim.x) {
+            const int h = it / upd, i = (it % upd) * 4;
+            const bool is_q = h < nq;
+            T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
+            const int base = h * d, nb = is_q ? base : base - NQ;
+            const float inv = is_q ? inv_q : inv_k;
+            const float* nw = is_q ? q_norm : k_norm;
+            auto normed4 = [&](int j, float (&o)[4]) {
+                float wv[4] = {1.f, 1.f, 1.f, 1.f};
+                load4(vals + base + j, o);
+                if (nw) load4(nw + nb + j, wv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] = o[k] * inv * wv[k];
+            };
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (i < half) {
+                float u[4], w2[4], hi[4];
+                normed4(i, u);
+                normed4(i + half, w2);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) rotate_pair(u[k], w2[k], trig[i + k], trig[half + i + k], r[k], hi[k]);
+                store4(dst + i + half, hi);
+            } else if (i < rot) {
+                continue;  // written by its partner
+            } else if (i < d) {
+                normed4(i, r);
+            }
+            store4(dst + i, r);
+        }
+        for (int it = threadIdx.x; it < nkv * upd; it += blockDim.x) {
+            const int h = it / upd, i = (it % upd) * 4;
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
+            if (i < dv) {
+                const int j = h * dv + i;
+                float bv[4] = {0.f, 0.f, 0.f, 0.f};
+                load4(row + NQ + NK + j, r);
+                if (bias) load4(bias + NQ + NK + j, bv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) r[k] += bv[k];
+                if (v_out) store4(v_out + (size_t)t * NV + j, r);
+                if (v_first) {
+                    float f[4];
+                    load4(v_first + (size_t)t * NV + j, f);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) r[k] = (1.f - lam) * r[k] + lam * f[k];
+                }
+            }
+            if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
+        }
+        return;
+    }
     // q and k: one item per (head, dim below dp); pairs of the rotated part are computed twice, once per half
     const int heads = nq + (page > 0 ? nkv : 0);
     for (int it = threadIdx.x; it < heads * dp; it += blockDim.x) {
@@ -234,7 +353,6 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias, co
         dst[i] = from_float<T>(r);
     }
     // values
-    const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
     for (int it = threadIdx.x; it < nkv * dp; it += blockDim.x) {
         const int h = it / dp, i = it % dp;
         float r = 0.f;
@@ -257,6 +375,9 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
     const size_t smem = ((size_t)(nq + nkv) * d + rot) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     const int threads = (nq + nkv) * d >= 1024 ? 256 : 128;
+    const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)v_first |
+                          (uintptr_t)v_out | (uintptr_t)q_out | (uintptr_t)cache;
+    const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % 8 == 0 && (all & 15) == 0;
     cudaError_t e;
     static size_t configured[2] = {0, 0};  // the attribute only ever grows (and is not set inside a capture again)
 #define PREP_CASE(TT, which) \
@@ -266,9 +387,10 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
             if (e != cudaSuccess) return (int)e; \
             configured[which] = smem; \
         } \
-        return (int)launch_kernel(qkv_prepare_kernel<TT>, T, threads, smem, stream, (const TT*)qkv, bias, q_norm, k_norm, eps, \
-                                  positions, token_entry, meta, group, inv_freq, rot, (const TT*)v_first, v_lambda, (TT*)v_out, \
-                                  (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, page_size, num_pages, store_kv, status); \
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT>, T, threads, smem, stream, (const TT*)qkv, bias, \
+                                      q_norm, k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, (const TT*)v_first, \
+                                      v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, page_size, num_pages, \
+                                      store_kv, vec4, status); \
     } while (0)
     if (dtype == DT_F32) PREP_CASE(float, 0);
     PREP_CASE(__nv_bfloat16, 1);
@@ -279,40 +401,80 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
 // out[t] = a N(z) + b N(z^2) + c N(z^3) + e with N(u) = u / sqrt(mean(u^2) + eps) over the row; powers element by
 // element; coef = (a, b, c, e).  The three mean squares are sums of z^2, z^4 and z^6, taken in one pass.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out,
-                const int* __restrict__ meta, int F) {
+                const int* __restrict__ meta, int F, int vec4) {
     __shared__ float red[33];
+    constexpr int MAXC = 8;  // up to 8 x 4 values a thread stay in registers between the two passes
     const float a = coef[0], b = coef[1], c = coef[2], e0 = coef[3];
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     if (meta && t >= meta[META_NUM_TOKENS]) return;
     const T* zr = z + (size_t)t * F;
     T* o = out + (size_t)t * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float v = to_float(zr[i]), v2 = v * v, v3 = v2 * v;
-        s2 += v2;
-        s4 = fmaf(v2, v2, s4);
-        s6 = fmaf(v3, v3, s6);
+    const bool in_regs = vec4 && F <= 4 * MAXC * (int)blockDim.x;
+    float v[MAXC][4];
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < MAXC; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < F) {
+                load4(zr + i, v[j]);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float v2 = v[j][k] * v[j][k], v3 = v2 * v[j][k];
+                    s2 += v2;
+                    s4 = fmaf(v2, v2, s4);
+                    s6 = fmaf(v3, v3, s6);
+                }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < F; i += blockDim.x) {
+            const float x = to_float(zr[i]), x2 = x * x, x3 = x2 * x;
+            s2 += x2;
+            s4 = fmaf(x2, x2, s4);
+            s6 = fmaf(x3, x3, s6);
+        }
     }
     s2 = block_sum(s2, red);
     s4 = block_sum(s4, red);
     s6 = block_sum(s6, red);
     const float n1 = a * rsqrtf(s2 / (float)F + eps), n2 = b * rsqrtf(s4 / (float)F + eps), n3 = c * rsqrtf(s6 / (float)F + eps);
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < MAXC; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < F) {
+                float r[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float x = v[j][k], x2 = x * x;
+                    r[k] = n1 * x + n2 * x2 + n3 * (x2 * x) + e0;
+                }
+                store4(o + i, r);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < F; i += blockDim.x) {
-        const float v = to_float(zr[i]), v2 = v * v;
-        o[i] = from_float<T>(n1 * v + n2 * v2 + n3 * (v2 * v) + e0);
+        const float x = to_float(zr[i]), x2 = x * x;
+        o[i] = from_float<T>(n1 * x + n2 * x2 + n3 * (x2 * x) + e0);
     }
 }
 
 extern "C" int polynorm(const void* z, int dtype, const float* coef, float eps, void* out, const int* meta, int T, int F,
                         cudaStream_t stream) {
     if (T <= 0) return 0;
-    const int threads = F >= 1024 ? 256 : 128;
+    const int vec4 = F % 4 == 0 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0;
+    // as many threads as keep a row in registers (32 values each), 128 at least and 1024 at most
+    int threads = ((F + 31) / 32 + 31) / 32 * 32;
+    threads = threads < 128 ? 128 : threads > 1024 ? 1024 : threads;
     if (dtype == DT_F32)
-        return (int)launch_kernel(polynorm_kernel<float>, T, threads, 0, stream, (const float*)z, coef, eps, (float*)out, meta, F);
-    return (int)launch_kernel(polynorm_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)z, coef, eps,
-                              (__nv_bfloat16*)out, meta, F);
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, polynorm_kernel<float>, T, threads, 0, stream, (const float*)z, coef, eps,
+                                      (float*)out, meta, F, vec4);
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, polynorm_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)z,
+                                  coef, eps, (__nv_bfloat16*)out, meta, F, vec4);
 }

@@ -320,7 +320,9 @@ def design_comparison(args) -> int:
 def design_kernels(rt, hbm, median_ms) -> None:
     """The Dosovik layers' own kernels beside Llama's like kernels, alone, at width 2048 / 32 heads of 64 / 8 key heads /
     feed-forward 8192: microseconds a call and the fraction of the copy bandwidth that the bytes each must move give.
-    Rows of 8,192 tokens (inputs and outputs beyond the L2) and of 8 tokens (a decode step; launch-bound)."""
+    Rows of 16,384 tokens (every kernel's inputs and outputs together exceed the L2) and of 8 tokens (a decode step:
+    the time of a launch inside a captured graph).  Each figure: 16 calls captured in one CUDA graph, CUDA events
+    around three replays, after three warm-up calls."""
     import torch
 
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -330,7 +332,25 @@ def design_kernels(rt, hbm, median_ms) -> None:
     H, I, nq, nkv, d, taps = 2048, 8192, 32, 8, 64, 4
     bf = torch.bfloat16
     print(f"kernels alone (copy bandwidth {hbm:.0f} GB/s): name, rows, us, bytes moved / time / copy bandwidth")
-    for T in (8192, 8):
+    def graph_us(fn, n=16):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(n):
+                fn()
+        gr.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(3):
+            gr.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (3 * n) * 1e3
+
+    for T in (16384, 8):
         entries = [(0, T)] if T > 64 else [(100 + i, 1) for i in range(T)]
         tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 0)
         ctx, _ = K.make_context(rt, entries, PAGE, tables)
@@ -365,10 +385,7 @@ def design_kernels(rt, hbm, median_ms) -> None:
                              lambda: ops.scaled_add_rmsnorm(resid, delta, 1.0, w, 1e-5, ctx, keep=(state, taps), conv=(cw, state, h2)),
                              T * H * (4 + 2 + 4 + 2)))
         for name, fn, nbytes in cases:
-            def many():
-                for _ in range(20):
-                    fn()
-            us = median_ms(many) / 20 * 1e3
+            us = graph_us(fn)
             print(f"  {name:62s} {T:5d} rows {us:8.1f} us  {nbytes / (us * 1e-6) / (hbm * 1e9):5.2f}")
         # attention: a prompt of T tokens (or T decode tokens over 2,048 cached ones), plain and with chunk mask + sink
         entries = [(0, T)] if T > 64 else [(2047, 1)] * T
@@ -378,10 +395,7 @@ def design_kernels(rt, hbm, median_ms) -> None:
         q, o = torch.randn(T, nq * d, device=dev).to(bf), torch.empty(T, nq * d, device=dev, dtype=bf)
         for name, kw in (("llama:   attention", {}), ("dosovik: attention, chunks of 1024 + sink", {"chunk": 1024, "sink": True}),
                          ("dosovik: attention, sink alone", {"sink": True})):
-            def many():
-                for _ in range(10):
-                    ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, 0, 0.125, **kw)
-            us = median_ms(many) / 10 * 1e3
+            us = graph_us(lambda: ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, 0, 0.125, **kw), n=4)
             print(f"  {name:62s} {T:5d} rows {us:8.1f} us")
     ops.check_status()
 
