@@ -5,9 +5,36 @@
 // reduction runs in an order that depends only on the row it belongs to.
 #include "common.cuh"
 
+// N sums over a block at once, in the fixed order of block_sum (warp shuffles, then warp 0 over the warp sums), with two
+// barriers for all of them.  `scratch` holds N * 33 floats in shared memory.  All threads get the results.
+template <int N>
+__device__ __forceinline__ void block_sums(float (&v)[N], float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int k = 0; k < N; ++k) v[k] = warp_sum(v[k]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) scratch[k * 33 + warp] = v[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            float t = lane < nwarps ? scratch[k * 33 + lane] : 0.f;
+            t = warp_sum(t);
+            if (lane == 0) scratch[k * 33 + 32] = t;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < N; ++k) v[k] = scratch[k * 33 + 32];
+}
+
 // ----------------------------------------------------------------------------- short convolution over time
-// What a sublayer reads: y[t] = x[t] * (1 or 0) + sum_j w[c, j] * x[t - taps + 1 + j], x the float32 residual
-// stream, zeros before the start of a request.  Rows before the step's portion come from the request's state: a
+// What a sublayer reads: y[t] = x[t] * (1 or 0) + sum_j w[j, c] * x[t - taps + 1 + j], x the float32 residual
+// stream, zeros before the start of a request; w is [taps, C] (the checkpoint's [C, taps] transposed once at load
+// time), so that the threads of a warp read neighbouring weights.  Rows before the step's portion come from the request's state: a
 // ring of R = taps - 1 rows per state slot (slot_stride floats from one slot to the next), the row of position p at
 // ring place p mod R.  The state is written by
 // short_conv_save (or by the norm kernel below) AFTER this kernel has read it: only the last R rows of an entry
@@ -26,15 +53,15 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
     const float* st = state + (size_t)slots[e] * slot_stride;
     if (vec4) {  // four channels a thread, 16-byte accesses (C a multiple of 4, buffers on 16 bytes)
         for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
-            const float* wc = w + (size_t)c * taps;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < taps; ++j) {  // oldest tap first: a fixed order
                 const int back = taps - 1 - j, src = p - back;
                 if (src < 0) continue;
-                float v[4];
+                float v[4], wv[4];
                 load4((t - back >= first) ? x + (size_t)(t - back) * C + c : st + (size_t)(src % R) * C + c, v);
+                load4(w + (size_t)j * C + c, wv);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) acc[i] = fmaf(wc[i * taps + j], v[i], acc[i]);
+                for (int i = 0; i < 4; ++i) acc[i] = fmaf(wv[i], v[i], acc[i]);
             }
             if (add_input) {
                 float v[4];
@@ -47,13 +74,12 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
         return;
     }
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float* wc = w + (size_t)c * taps;
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {  // oldest tap first: a fixed order
             const int back = taps - 1 - j, src = p - back;
             if (src < 0) continue;
             const float v = (t - back >= first) ? x[(size_t)(t - back) * C + c] : st[(size_t)(src % R) * C + c];
-            acc = fmaf(wc[j], v, acc);
+            acc = fmaf(w[(size_t)j * C + c], v, acc);
         }
         if (add_input) acc += x[(size_t)t * C + c];
         y[(size_t)t * C + c] = from_float<TO>(acc);
@@ -65,7 +91,7 @@ extern "C" int short_conv(const float* x, const float* w, const float* state, vo
                           int C, int taps, int add_input, long long slot_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = C >= 1024 ? 256 : 128;
-    const int vec4 = C % 4 == 0 && slot_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)state | (uintptr_t)y) & 15) == 0;
+    const int vec4 = C % 4 == 0 && slot_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)state | (uintptr_t)y | (uintptr_t)w) & 15) == 0;
     if (y_dtype == DT_F32)
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, short_conv_kernel<float>, T, threads, 0, stream, x, w, state, (float*)y, meta, positions,
                                   token_entry, cu_tokens, slots, C, taps, add_input, slot_stride, vec4);
@@ -171,14 +197,13 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const float v = row[i] * inv * w[i];
         x[i] = v;
-        if (conv_out) {
-            const float* wc = conv_w + (size_t)i * conv_taps;
+        if (conv_out) {  // conv_w is [taps, H]
             float acc = 0.f;
             for (int j = 0; j < R; ++j) {
                 const int src = p - (R - j);
-                if (src >= 0) acc = fmaf(wc[j], st[(size_t)(src % R) * H + i], acc);
+                if (src >= 0) acc = fmaf(conv_w[(size_t)j * H + i], st[(size_t)(src % R) * H + i], acc);
             }
-            acc = fmaf(wc[R], v, acc);
+            acc = fmaf(conv_w[(size_t)R * H + i], v, acc);
             conv_out[(size_t)t * H + i] = from_float<TO>(acc + v);
         }
     }
@@ -226,7 +251,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias, co
                    T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
                    int store_kv, int vec4, int* __restrict__ status) {
     extern __shared__ __align__(16) float vals[];  // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
-    __shared__ float red[33];
+    __shared__ float red[66];
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -254,8 +279,12 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias, co
         }
     }
     float inv_q = 1.f, inv_k = 1.f;
-    if (q_norm) inv_q = rsqrtf(block_sum(sq, red) / (float)NQ + eps);
-    if (k_norm) inv_k = rsqrtf(block_sum(sk, red) / (float)NK + eps);
+    if (q_norm || k_norm) {
+        float both[2] = {sq, sk};
+        block_sums<2>(both, red);
+        if (q_norm) inv_q = rsqrtf(both[0] / (float)NQ + eps);
+        if (k_norm) inv_k = rsqrtf(both[1] / (float)NK + eps);
+    }
     const int pos = positions[t], half = rot / 2;
     float* trig = vals + NQ + NK;
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
@@ -404,7 +433,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out,
                 const int* __restrict__ meta, int F, int vec4) {
-    __shared__ float red[33];
+    __shared__ float red[99];
     constexpr int MAXC = 8;  // up to 8 x 4 values a thread stay in registers between the two passes
     const float a = coef[0], b = coef[1], c = coef[2], e0 = coef[3];
     pdl_wait();
@@ -439,10 +468,10 @@ polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float e
             s6 = fmaf(x3, x3, s6);
         }
     }
-    s2 = block_sum(s2, red);
-    s4 = block_sum(s4, red);
-    s6 = block_sum(s6, red);
-    const float n1 = a * rsqrtf(s2 / (float)F + eps), n2 = b * rsqrtf(s4 / (float)F + eps), n3 = c * rsqrtf(s6 / (float)F + eps);
+    float sums[3] = {s2, s4, s6};
+    block_sums<3>(sums, red);
+    const float n1 = a * rsqrtf(sums[0] / (float)F + eps), n2 = b * rsqrtf(sums[1] / (float)F + eps),
+                n3 = c * rsqrtf(sums[2] / (float)F + eps);
     if (in_regs) {
 #pragma unroll
         for (int j = 0; j < MAXC; ++j) {

@@ -347,10 +347,11 @@ class CudaOps:
         return ctypes.c_longlong(state.stride(0))
 
     def short_conv(self, x, w, state, ctx, out, *, add_input: bool = True):
-        """out[t] = (x[t] +) sum_j w[:, j] * x[t - taps + 1 + j] over the float32 residual rows of each request, zeros
-        before its start; rows before the step's portion come from ``state`` (float32 [slots, taps - 1, C], the row of
-        position p at place p mod (taps - 1); None when taps is 1).  ``short_conv_save`` writes the state afterwards."""
-        C, taps = w.shape
+        """out[t] = (x[t] +) sum_j w[j] * x[t - taps + 1 + j] over the float32 residual rows of each request, zeros
+        before its start; ``w`` is float32 [taps, C]; rows before the step's portion come from ``state`` (float32
+        [slots, taps - 1, C], the row of position p at place p mod (taps - 1); None when taps is 1).
+        ``short_conv_save`` writes the state afterwards."""
+        taps, C = w.shape
         self._check(self.lib.short_conv(_p(x), _p(w), _p(state), _p(out), _code(out), _p(ctx.meta), _p(ctx.positions),
                                         _p(ctx.token_entry), _p(ctx.cu_tokens), _p(ctx.state_slots), ctx.T, C, taps,
                                         int(add_input), self._slot_stride(state), self._stream()), "short_conv")
@@ -365,8 +366,8 @@ class CudaOps:
     def scaled_add_rmsnorm(self, resid, delta, alpha: float, w, eps: float, ctx, *, keep=None, conv=None):
         """The norm after the sum: resid <- rmsnorm(alpha * resid + delta) * w, in place, float32.
         ``keep=(state, taps)``: the rows as they were before go to that convolution state (the last taps - 1 of every
-        entry).  ``conv=(w, state, out)``, decode steps only: also out <- new row + short convolution of it over
-        ``state``, the input of the sublayer that follows."""
+        entry).  ``conv=(w [taps, H], state, out)``, decode steps only: also out <- new row + short convolution of it
+        over ``state``, the input of the sublayer that follows."""
         H = resid.shape[1]
         k_state, k_taps = keep if keep is not None else (None, 0)
         c_w, c_state, c_out = conv if conv is not None else (None, None, None)
@@ -375,7 +376,7 @@ class CudaOps:
                                                 _p(k_state), int(k_taps), self._slot_stride(k_state), self._slot_stride(c_state),
                                                 _p(ctx.positions), _p(ctx.token_entry),
                                                 _p(ctx.cu_tokens), _p(ctx.state_slots), _p(c_w), _p(c_state),
-                                                c_w.shape[1] if c_w is not None else 0, _p(c_out),
+                                                c_w.shape[0] if c_w is not None else 0, _p(c_out),
                                                 _code(c_out) if c_out is not None else DT_F32, self._stream()),
                     "scaled_add_rmsnorm")
 

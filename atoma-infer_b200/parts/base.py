@@ -207,7 +207,10 @@ class Block(Part):
     ``forward(resid, delta, ctx, cache)``: ``resid`` is the float32 residual stream
     [T, H], ``delta`` what the previous block left to be added (None at the first);
     returns this block's own pending addition.  Keeping the last addition pending lets
-    the next norm do it, in float32, in the same pass."""
+    the next norm do it, in float32, in the same pass.  ``ctx.shared["next_run"]`` holds
+    (block, cache view) of the layer run that follows, or None: a block whose last kernel can
+    also leave that block's input may do so under ``ctx.shared["prepared_input"]`` =
+    (that block, tensor), which the next block takes if it finds itself named."""
 
     mixer: Mixer
 

@@ -130,9 +130,13 @@ class PostNormBlock(Block):
         s1, s2 = self._share(cache.state, "filter1"), self._share(cache.state, "filter2")
         # decode steps: the norm kernel also leaves the next sublayer's input (new row + its short convolution)
         f2 = self.filter2.fused() if self.filter2 is not None else None
-        fuse = (ctx.decode_only and ctx.T == ctx.S and f2 is not None and f2["kind"] == "short_conv" and f2["add_input"]
-                and getattr(ops, "fused_post_norm", True))
-        h = self.filter1.forward(resid, ctx, s1) if self.filter1 is not None else self._plain_input(resid)
+        decode = ctx.decode_only and ctx.T == ctx.S and getattr(ops, "fused_post_norm", True)
+        fuse = decode and f2 is not None and f2["kind"] == "short_conv" and f2["add_input"]
+        ready = ctx.shared.pop("prepared_input", None)  # the block before may have left this block's input
+        if ready is not None and ready[0] is self:
+            h = ready[1]
+        else:
+            h = self.filter1.forward(resid, ctx, s1) if self.filter1 is not None else self._plain_input(resid)
         a = self.mixer.forward(h, ctx, mixer_cache)
         keep1 = (self.filter1.ring(s1), self.filter1.taps) if self.filter1 is not None else None
         h2 = None
@@ -143,12 +147,22 @@ class PostNormBlock(Block):
         else:
             self.norm1.forward_post(resid, a, self.alpha, ctx, keep=keep1)
         if self.feed_forward is None:
-            return None
+            return None  # (a layer with one sum leaves the next block's input to that block)
         if h2 is None:
             h2 = self.filter2.forward(resid, ctx, s2) if self.filter2 is not None else self._plain_input(resid)
         f = self.feed_forward.forward(h2, ctx)
         keep2 = (self.filter2.ring(s2), self.filter2.taps) if self.filter2 is not None else None
-        self.norm2.forward_post(resid, f, self.alpha, ctx, keep=keep2)
+        conv = None
+        nxt = ctx.shared.get("next_run")
+        if decode and nxt is not None and isinstance(nxt[0], PostNormBlock) and nxt[0].filter1 is not None:
+            # decode steps: this norm also leaves the next block's input, the new row + that block's first convolution
+            blk, view = nxt
+            f1 = blk.filter1.fused()
+            if f1["kind"] == "short_conv" and f1["add_input"] and view.state is not None:
+                hn = torch.empty((ctx.T, resid.shape[1]), dtype=self.rt.dtype, device=resid.device)
+                conv = (f1["weight"], blk.filter1.ring(blk._share(view.state, "filter1")), hn)
+                ctx.shared["prepared_input"] = (blk, hn)
+        self.norm2.forward_post(resid, f, self.alpha, ctx, keep=keep2, conv=conv)
         return None
 
     def _plain_input(self, resid):

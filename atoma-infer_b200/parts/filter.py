@@ -30,7 +30,8 @@ class ShortConv(SequenceFilter):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.weight = tensors[self.prefix].to(torch.float32).contiguous()  # exact widening
+        # widened exactly; kept as [taps, channels] so that neighbouring threads of the kernels read neighbouring weights
+        self.weight = tensors[self.prefix].to(torch.float32).t().contiguous()
 
     def state_bytes(self):
         return (self.taps - 1) * self.channels * 4

@@ -176,6 +176,8 @@ class DecoderModel:
                 stack.forward_chain(resid, delta, ctx, [view_of(k) for k in range(stack.first, stack.end)])
                 delta, i = None, stack.end
                 continue
+            # what runs next, for a block whose last kernel can also leave the next block's input (see Block.forward)
+            ctx.shared["next_run"] = (self.blocks[self.runs[i + 1].layer], view_of(i + 1)) if i + 1 < len(self.runs) else None
             delta = self.blocks[self.runs[i].layer].forward(resid, delta, ctx, view_of(i))
             i += 1
         if num_rows == 0:

@@ -356,7 +356,7 @@ def design_kernels(rt, hbm, median_ms) -> None:
         ctx, _ = K.make_context(rt, entries, PAGE, tables)
         resid, delta = torch.randn(T, H, device=dev), torch.randn(T, H, device=dev).to(bf)
         w = torch.ones(H, device=dev)
-        cw, state = torch.randn(H, taps, device=dev), torch.zeros(max(len(entries), 1), taps - 1, H, device=dev)
+        cw, state = torch.randn(taps, H, device=dev), torch.zeros(max(len(entries), 1), taps - 1, H, device=dev)
         out = torch.empty(T, H, device=dev, dtype=bf)
         qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(bf)
         cache = torch.zeros(num_pages, 2, nkv, PAGE, d, device=dev, dtype=bf)

@@ -102,7 +102,7 @@ class HostOps:
 
     def short_conv(self, x, w, state, ctx, out, *, add_input=True):
         self._count()
-        taps = w.shape[1]
+        taps, w = w.shape[0], w.t()  # the kernels take [taps, channels]
         for _, a, b, slot in self._entries(ctx):
             p0 = int(ctx.positions[a])
             past = [state[slot, p % (taps - 1)] if p >= 0 else torch.zeros_like(x[0]) for p in range(p0 - taps + 1, p0)]

@@ -92,3 +92,33 @@ def test_generation_through_the_engine(dtype, models):
             row = logits[len(p) - 1 + i]
             lead = float(row.max() - row[tok]) / float(row.abs().max())
             assert lead <= 2 * helpers.BF16_TOL, (i, tok, lead)
+
+
+def test_the_command_line_serves_the_design(tmp_path):
+    """``random-model`` writes a Dosovik folder from its configuration, ``generate`` decodes greedily from it; both as
+    child processes, the tokens against the plain loop (float32)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    cli = os.path.join(helpers.ROOT, "bin", "atoma-infer")
+    cfg, page = DH.CONFIGS["Q"]
+    (tmp_path / "config_in.json").write_text(json.dumps(cfg))
+    out = tmp_path / "model"
+
+    def run(args):
+        p = subprocess.run([sys.executable, cli, *args], capture_output=True, text=True, timeout=900)
+        assert p.returncode == 0, f"atoma-infer {' '.join(args)} failed ({p.returncode}):\n{p.stdout[-2000:]}\n{p.stderr[-4000:]}"
+        return p
+
+    run(["random-model", "--config", str(tmp_path / "config_in.json"), "--seed", "7", "--out", str(out), "--std", "0.05",
+         "--norm-jitter", "0.1"])
+    prompts = [[3, 14, 15, 92, 65, 35, 89, 79], list(range(40, 95))]
+    args = ["generate", "--model", str(out), "--dtype", "f32", "--block-size", str(page), "--num-gpu-blocks-override", "16",
+            "--max-num-batched-tokens", "24", "--max-num-sequences", "2", "--no-do-sample", "--max-new-tokens", "8",
+            "--ignore-eos-token"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    recs = [json.loads(line) for line in run(args).stdout.splitlines() if line.startswith("{")]
+    assert [r["token_ids"] for r in recs] == [DH.plain_greedy(str(out), cfg, p, 8) for p in prompts]

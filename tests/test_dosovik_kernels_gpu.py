@@ -37,7 +37,7 @@ def test_short_conv_over_portions_and_slots(rts, taps, C):
     R = taps - 1
     wide = torch.full((3, 7 + R * C + 5), float("nan"), device=rt.device)  # NaN: a row read before it was written shows
     state = wide[:, 7:7 + R * C].unflatten(1, (R, C)) if R else None
-    wd = w.to(rt.device)
+    wd = w.t().contiguous().to(rt.device)  # the kernels take [taps, channels]
     at = [0, 0, 0]
     sizes = [1, 2, 9, 3, 1, 1, 4, 2]
     step = 0
@@ -100,7 +100,7 @@ def test_norm_after_the_sum_leaves_the_next_input_in_decode_steps(rts):
     entries = [(0, 1), (1, 1), (2, 1), (9, 1)]  # the first positions of a request: rows before its start are zeros
     ctx, _ = K.make_context(rt, entries, 16, [[1]] * 4)
     x, d = torch.randn(4, H, generator=g).to(rt.device), torch.randn(4, H, generator=g).to(rt.device)
-    w, cw = (1 + 0.1 * torch.randn(H, generator=g)).to(rt.device), torch.randn(H, taps, generator=g).to(rt.device)
+    w, cw = (1 + 0.1 * torch.randn(H, generator=g)).to(rt.device), torch.randn(taps, H, generator=g).to(rt.device)
     state = torch.randn(4, taps - 1, H, generator=g).to(rt.device)
     for dtype in (torch.float32, torch.bfloat16):
         a, b = x.clone(), x.clone()
@@ -112,7 +112,7 @@ def test_norm_after_the_sum_leaves_the_next_input_in_decode_steps(rts):
         assert torch.equal(a, b)
         assert torch.allclose(fused.float(), apart.float(), atol=1e-5 if dtype == torch.float32 else 2e-2)
     # position 0 sees only itself, whatever the ring holds
-    want0 = b[0] * (1 + cw[:, taps - 1])
+    want0 = b[0] * (1 + cw[taps - 1])
     assert torch.allclose(apart[0].float(), want0, atol=3e-2)
 
 
