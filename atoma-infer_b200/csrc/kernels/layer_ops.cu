@@ -144,7 +144,7 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
                           const float* __restrict__ conv_w, const float* __restrict__ conv_state, int conv_taps,
                           TO* __restrict__ conv_out, int vec4) {
     __shared__ float red[33];
-    extern __shared__ __align__(16) float row[];  // H floats
+    extern __shared__ __align__(16) float row[];  // H floats, and H more with conv_out
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -155,6 +155,12 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
     float* kept = nullptr;
     if (keep && keeps_row(t, e, cu_tokens, keep_rows))
         kept = keep + (size_t)slots[e] * keep_stride + (size_t)(positions[t] % keep_rows) * H;
+    // The part of the next sublayer's convolution that comes from its state does not depend on this norm: it is taken
+    // in the first pass, with the loads of the row, and waits in shared memory behind the row.
+    const int R = conv_taps - 1;
+    const int p = conv_out ? positions[t] : 0;
+    const float* st = conv_out ? conv_state + (size_t)slots[e] * conv_stride : nullptr;
+    float* pre = row + H;
     float ss = 0.f;
     if (vec4) {  // four values a thread, 16-byte accesses; the sum's order differs from the scalar form's, but is as fixed
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
@@ -162,6 +168,19 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
             load4(x + i, old);
             if (kept) store4(kept + i, old);
             if (dl) load4(dl + i, d);
+            if (conv_out) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int j = 0; j < R; ++j) {
+                    const int src = p - (R - j);
+                    if (src < 0) continue;
+                    float sv[4], wv[4];
+                    load4(st + (size_t)(src % R) * H + i, sv);
+                    load4(conv_w + (size_t)j * H + i, wv);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc[k] = fmaf(wv[k], sv[k], acc[k]);
+                }
+                store4(pre + i, acc);
+            }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 v[k] = dl ? fmaf(alpha, old[k], d[k]) : alpha * old[k];
@@ -173,6 +192,14 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             const float old = x[i];
             if (kept) kept[i] = old;
+            if (conv_out) {
+                float acc = 0.f;
+                for (int j = 0; j < R; ++j) {
+                    const int src = p - (R - j);
+                    if (src >= 0) acc = fmaf(conv_w[(size_t)j * H + i], st[(size_t)(src % R) * H + i], acc);
+                }
+                pre[i] = acc;
+            }
             const float v = dl ? fmaf(alpha, old, to_float(dl[i])) : alpha * old;
             row[i] = v;
             ss = fmaf(v, v, ss);
@@ -180,10 +207,7 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)H + eps);
-    const int R = conv_taps - 1;
-    const int p = conv_out ? positions[t] : 0;
-    const float* st = conv_out ? conv_state + (size_t)slots[e] * conv_stride : nullptr;
-    if (vec4 && !conv_out) {
+    if (vec4) {
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             float v[4], wv[4];
             load4(row + i, v);
@@ -191,21 +215,21 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
 #pragma unroll
             for (int k = 0; k < 4; ++k) v[k] = v[k] * inv * wv[k];
             store4(x + i, v);
+            if (conv_out) {  // conv_w is [taps, H]; its last row is the tap of the new row itself
+                float acc[4], cw[4];
+                load4(pre + i, acc);
+                load4(conv_w + (size_t)R * H + i, cw);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = fmaf(cw[k], v[k], acc[k]) + v[k];
+                store4(conv_out + (size_t)t * H + i, acc);
+            }
         }
         return;
     }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const float v = row[i] * inv * w[i];
         x[i] = v;
-        if (conv_out) {  // conv_w is [taps, H]
-            float acc = 0.f;
-            for (int j = 0; j < R; ++j) {
-                const int src = p - (R - j);
-                if (src >= 0) acc = fmaf(conv_w[(size_t)j * H + i], st[(size_t)(src % R) * H + i], acc);
-            }
-            acc = fmaf(conv_w[(size_t)R * H + i], v, acc);
-            conv_out[(size_t)t * H + i] = from_float<TO>(acc + v);
-        }
+        if (conv_out) conv_out[(size_t)t * H + i] = from_float<TO>(fmaf(conv_w[(size_t)R * H + i], v, pre[i]) + v);
     }
 }
 
@@ -217,17 +241,26 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
                                   cudaStream_t stream) {
     if (n <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    const size_t smem = (size_t)H * sizeof(float);
+    const size_t smem = (size_t)H * sizeof(float) * (conv_out ? 2 : 1);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    static size_t configured[4] = {0, 0, 0, 0};  // per instantiation; grows only, and is not set inside a capture again
     if (keep_taps <= 1) keep = nullptr;
-    const int vec4 = H % 4 == 0 && keep_stride % 4 == 0 && (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)keep) & 15) == 0;
-#define POSTNORM_CASE(TD, TO) \
+    const int vec4 = H % 4 == 0 && keep_stride % 4 == 0 && conv_stride % 4 == 0 &&
+                     (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)keep | (uintptr_t)conv_w |
+                       (uintptr_t)conv_state | (uintptr_t)conv_out) & 15) == 0;
+#define POSTNORM_CASE(TD, TO, which) \
+    if (smem > 48 * 1024 && smem > configured[which]) { \
+        cudaError_t e = cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e; \
+        configured[which] = smem; \
+    } \
     return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, scaled_add_rmsnorm_kernel<TD, TO>, n, threads, smem, stream, resid, \
                                   (const TD*)delta, alpha, w, eps, meta, H, keep, keep_taps - 1, keep_stride, conv_stride, positions, token_entry, \
                                   cu_tokens, slots, conv_w, conv_state, conv_taps, (TO*)conv_out, vec4)
-    if (delta_dtype == DT_F32 && conv_out_dtype == DT_F32) POSTNORM_CASE(float, float);
-    else if (delta_dtype == DT_F32) POSTNORM_CASE(float, __nv_bfloat16);
-    else if (conv_out_dtype == DT_F32) POSTNORM_CASE(__nv_bfloat16, float);
-    else POSTNORM_CASE(__nv_bfloat16, __nv_bfloat16);
+    if (delta_dtype == DT_F32 && conv_out_dtype == DT_F32) { POSTNORM_CASE(float, float, 0); }
+    else if (delta_dtype == DT_F32) { POSTNORM_CASE(float, __nv_bfloat16, 1); }
+    else if (conv_out_dtype == DT_F32) { POSTNORM_CASE(__nv_bfloat16, float, 2); }
+    else { POSTNORM_CASE(__nv_bfloat16, __nv_bfloat16, 3); }
 #undef POSTNORM_CASE
 }
 
@@ -243,155 +276,175 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
 //    the tail is zeros, so that kernels that use one head size for keys and values can read them).
 template <typename T>
 __global__ void __launch_bounds__(256)
-qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias, const float* __restrict__ q_norm,
-                   const float* __restrict__ k_norm, float eps, const int* __restrict__ positions,
+qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, const float* __restrict__ q_norm_g,
+                   const float* __restrict__ k_norm_g, float eps, const int* __restrict__ positions,
                    const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
                    const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
                    const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
                    T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
-                   int store_kv, int vec4, int* __restrict__ status) {
-    extern __shared__ __align__(16) float vals[];  // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
+                   int store_kv, int vec4, int tokens_per_block, int* __restrict__ status) {
+    // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token; with several tokens a block also the
+    // biases and the norm weights, fetched once for all of them
+    extern __shared__ __align__(16) float vals[];
     __shared__ float red[66];
     pdl_wait();
     pdl_launch_dependents();
-    const int t = blockIdx.x;
-    if (t >= meta[META_NUM_TOKENS]) return;
-    const int NQ = nq * d, NK = nkv * d, NV = nkv * dv;
-    const T* row = qkv + (size_t)t * (NQ + NK + NV);
-    float sq = 0.f, sk = 0.f;
-    if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
-        for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
-            float v[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
-            load4(row + i, v);
-            if (bias) load4(bias + i, bv);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                v[k] += bv[k];
-                if (i < NQ) sq = fmaf(v[k], v[k], sq); else sk = fmaf(v[k], v[k], sk);
-            }
-            store4(vals + i, v);
-        }
-    } else {
-        for (int i = threadIdx.x; i < NQ + NK; i += blockDim.x) {
-            const float v = to_float(row[i]) + (bias ? bias[i] : 0.f);
-            vals[i] = v;
-            if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
-        }
-    }
-    float inv_q = 1.f, inv_k = 1.f;
-    if (q_norm || k_norm) {
-        float both[2] = {sq, sk};
-        block_sums<2>(both, red);
-        if (q_norm) inv_q = rsqrtf(both[0] / (float)NQ + eps);
-        if (k_norm) inv_k = rsqrtf(both[1] / (float)NK + eps);
-    }
-    const int pos = positions[t], half = rot / 2;
+    const int num_tokens = meta[META_NUM_TOKENS];
+    const int t_begin = blockIdx.x * tokens_per_block, t_end = min(t_begin + tokens_per_block, num_tokens);
+    if (t_begin >= t_end) return;
+    const int NQ = nq * d, NK = nkv * d, NV = nkv * dv, half = rot / 2;
     float* trig = vals + NQ + NK;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
-    int page = 0;
-    if (store_kv) {
-        const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
-        page = bt[pos / page_size];
-        if (page <= 0 || page >= num_pages) {
-            if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
-            page = 0;  // keys and values are dropped; the queries are still prepared
+    const float *bias = bias_g, *q_norm = q_norm_g, *k_norm = k_norm_g;
+    if (tokens_per_block > 1) {
+        float* sb = trig + rot;
+        float* sq = sb + (NQ + NK + NV);
+        float* sk = sq + NQ;
+        for (int i = threadIdx.x; i < NQ + NK + NV; i += blockDim.x) {
+            if (bias_g) sb[i] = bias_g[i];
+            if (i < NQ && q_norm_g) sq[i] = q_norm_g[i];
+            if (i < NK && k_norm_g) sk[i] = k_norm_g[i];
         }
+        if (bias_g) bias = sb;
+        if (q_norm_g) q_norm = sq;
+        if (k_norm_g) k_norm = sk;
     }
-    __syncthreads();
-    const int slot = pos % page_size;
-    const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
-    T* kpage = cache + (size_t)page * 2 * kv_block + (size_t)slot * dp;
-    T* vpage = kpage + kv_block;
     const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
-    if (vec4) {
-        // q and k: one item per (head, four dims); an item of the rotated part's first half also makes its partner
-        const int upd = dp / 4, heads = nq + (page > 0 ? nkv : 0);
-        for (int it = threadIdx.x; it < heads * upd; it += blockDim.x) {
-            const int h = it / upd, i = (it % upd) * 4;
+    const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
+    for (int t = t_begin; t < t_end; ++t) {
+        __syncthreads();  // the staged weights are written; the token before is done with vals and trig
+        const T* row = qkv + (size_t)t * (NQ + NK + NV);
+        const int pos = positions[t];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
+        int page = 0;
+        if (store_kv) {
+            const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
+            page = bt[pos / page_size];
+            if (page <= 0 || page >= num_pages) {
+                if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+                page = 0;  // keys and values are dropped; the queries are still prepared
+            }
+        }
+        float sq = 0.f, sk = 0.f;
+        if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
+            for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
+                float v[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
+                load4(row + i, v);
+                if (bias) load4(bias + i, bv);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    v[k] += bv[k];
+                    if (i < NQ) sq = fmaf(v[k], v[k], sq); else sk = fmaf(v[k], v[k], sk);
+                }
+                store4(vals + i, v);
+            }
+        } else {
+            for (int i = threadIdx.x; i < NQ + NK; i += blockDim.x) {
+                const float v = to_float(row[i]) + (bias ? bias[i] : 0.f);
+                vals[i] = v;
+                if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+            }
+        }
+        float inv_q = 1.f, inv_k = 1.f;
+        if (q_norm || k_norm) {  // (its barriers also publish vals and trig)
+            float both[2] = {sq, sk};
+            block_sums<2>(both, red);
+            if (q_norm) inv_q = rsqrtf(both[0] / (float)NQ + eps);
+            if (k_norm) inv_k = rsqrtf(both[1] / (float)NK + eps);
+        } else {
+            __syncthreads();
+        }
+        const int slot = pos % page_size;
+        T* kpage = cache + (size_t)page * 2 * kv_block + (size_t)slot * dp;
+        T* vpage = kpage + kv_block;
+        const int heads = nq + (page > 0 ? nkv : 0);
+        if (vec4) {
+            // q and k: one item per (head, four dims); an item of the rotated part's first half also makes its partner
+            const int upd = dp / 4;
+            for (int it = threadIdx.x; it < heads * upd; it += blockDim.x) {
+                const int h = it / upd, i = (it % upd) * 4;
+                const bool is_q = h < nq;
+                T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
+                const int base = h * d, nb = is_q ? base : base - NQ;  // k heads follow the q heads in vals
+                const float inv = is_q ? inv_q : inv_k;
+                const float* nw = is_q ? q_norm : k_norm;
+                auto normed4 = [&](int j, float (&o)[4]) {
+                    float wv[4] = {1.f, 1.f, 1.f, 1.f};
+                    load4(vals + base + j, o);
+                    if (nw) load4(nw + nb + j, wv);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[k] = o[k] * inv * wv[k];
+                };
+                float r[4] = {0.f, 0.f, 0.f, 0.f};
+                if (i < half) {
+                    float u[4], w2[4], hi[4];
+                    normed4(i, u);
+                    normed4(i + half, w2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) rotate_pair(u[k], w2[k], trig[i + k], trig[half + i + k], r[k], hi[k]);
+                    store4(dst + i + half, hi);
+                } else if (i < rot) {
+                    continue;  // written by its partner
+                } else if (i < d) {
+                    normed4(i, r);
+                }
+                store4(dst + i, r);
+            }
+            for (int it = threadIdx.x; it < nkv * upd; it += blockDim.x) {
+                const int h = it / upd, i = (it % upd) * 4;
+                float r[4] = {0.f, 0.f, 0.f, 0.f};
+                if (i < dv) {
+                    const int j = h * dv + i;
+                    float bv[4] = {0.f, 0.f, 0.f, 0.f};
+                    load4(row + NQ + NK + j, r);
+                    if (bias) load4(bias + NQ + NK + j, bv);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) r[k] += bv[k];
+                    if (v_out) store4(v_out + (size_t)t * NV + j, r);
+                    if (v_first) {
+                        float f[4];
+                        load4(v_first + (size_t)t * NV + j, f);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) r[k] = (1.f - lam) * r[k] + lam * f[k];
+                    }
+                }
+                if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
+            }
+            continue;
+        }
+        // q and k: one item per (head, dim below dp); pairs of the rotated part are computed twice, once per half
+        for (int it = threadIdx.x; it < heads * dp; it += blockDim.x) {
+            const int h = it / dp, i = it % dp;
             const bool is_q = h < nq;
             T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
-            const int base = h * d, nb = is_q ? base : base - NQ;
-            const float inv = is_q ? inv_q : inv_k;
-            const float* nw = is_q ? q_norm : k_norm;
-            auto normed4 = [&](int j, float (&o)[4]) {
-                float wv[4] = {1.f, 1.f, 1.f, 1.f};
-                load4(vals + base + j, o);
-                if (nw) load4(nw + nb + j, wv);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) o[k] = o[k] * inv * wv[k];
-            };
-            float r[4] = {0.f, 0.f, 0.f, 0.f};
-            if (i < half) {
-                float u[4], w2[4], hi[4];
-                normed4(i, u);
-                normed4(i + half, w2);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) rotate_pair(u[k], w2[k], trig[i + k], trig[half + i + k], r[k], hi[k]);
-                store4(dst + i + half, hi);
-            } else if (i < rot) {
-                continue;  // written by its partner
-            } else if (i < d) {
-                normed4(i, r);
-            }
-            store4(dst + i, r);
-        }
-        for (int it = threadIdx.x; it < nkv * upd; it += blockDim.x) {
-            const int h = it / upd, i = (it % upd) * 4;
-            float r[4] = {0.f, 0.f, 0.f, 0.f};
-            if (i < dv) {
-                const int j = h * dv + i;
-                float bv[4] = {0.f, 0.f, 0.f, 0.f};
-                load4(row + NQ + NK + j, r);
-                if (bias) load4(bias + NQ + NK + j, bv);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) r[k] += bv[k];
-                if (v_out) store4(v_out + (size_t)t * NV + j, r);
-                if (v_first) {
-                    float f[4];
-                    load4(v_first + (size_t)t * NV + j, f);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) r[k] = (1.f - lam) * r[k] + lam * f[k];
+            float r = 0.f;
+            if (i < d) {
+                const int base = h * d;
+                const float inv = is_q ? inv_q : inv_k;
+                const float* nw = is_q ? q_norm : k_norm;
+                const int nb = is_q ? base : base - NQ;
+                auto normed = [&](int j) { return vals[base + j] * inv * (nw ? nw[nb + j] : 1.f); };
+                if (i < rot) {
+                    const int f = i < half ? i : i - half;
+                    float lo, hi;
+                    rotate_pair(normed(f), normed(f + half), trig[f], trig[half + f], lo, hi);
+                    r = i < half ? lo : hi;
+                } else {
+                    r = normed(i);
                 }
             }
-            if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
+            dst[i] = from_float<T>(r);
         }
-        return;
-    }
-    // q and k: one item per (head, dim below dp); pairs of the rotated part are computed twice, once per half
-    const int heads = nq + (page > 0 ? nkv : 0);
-    for (int it = threadIdx.x; it < heads * dp; it += blockDim.x) {
-        const int h = it / dp, i = it % dp;
-        const bool is_q = h < nq;
-        T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
-        float r = 0.f;
-        if (i < d) {
-            const int base = h * d;  // k heads follow the q heads in vals
-            const float inv = is_q ? inv_q : inv_k;
-            const float* nw = is_q ? q_norm : k_norm;
-            const int nb = is_q ? base : base - NQ;
-            auto normed = [&](int j) { return vals[base + j] * inv * (nw ? nw[nb + j] : 1.f); };
-            if (i < rot) {
-                const int f = i < half ? i : i - half;
-                float lo, hi;
-                rotate_pair(normed(f), normed(f + half), trig[f], trig[half + f], lo, hi);
-                r = i < half ? lo : hi;
-            } else {
-                r = normed(i);
+        for (int it = threadIdx.x; it < nkv * dp; it += blockDim.x) {
+            const int h = it / dp, i = it % dp;
+            float r = 0.f;
+            if (i < dv) {
+                const int j = h * dv + i;
+                r = to_float(row[NQ + NK + j]) + (bias ? bias[NQ + NK + j] : 0.f);
+                if (v_out) v_out[(size_t)t * NV + j] = from_float<T>(r);
+                if (v_first) r = (1.f - lam) * r + lam * to_float(v_first[(size_t)t * NV + j]);
             }
+            if (page > 0) vpage[(size_t)h * head_block + i] = from_float<T>(r);
         }
-        dst[i] = from_float<T>(r);
-    }
-    // values
-    for (int it = threadIdx.x; it < nkv * dp; it += blockDim.x) {
-        const int h = it / dp, i = it % dp;
-        float r = 0.f;
-        if (i < dv) {
-            const int j = h * dv + i;
-            r = to_float(row[NQ + NK + j]) + (bias ? bias[NQ + NK + j] : 0.f);
-            if (v_out) v_out[(size_t)t * NV + j] = from_float<T>(r);
-            if (v_first) r = (1.f - lam) * r + lam * to_float(v_first[(size_t)t * NV + j]);
-        }
-        if (page > 0) vpage[(size_t)h * head_block + i] = from_float<T>(r);
     }
 }
 
@@ -401,7 +454,12 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
                            int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages, int store_kv, int* status,
                            cudaStream_t stream) {
     if (T <= 0) return 0;
-    const size_t smem = ((size_t)(nq + nkv) * d + rot) * sizeof(float);
+    const size_t row_floats = (size_t)(nq + nkv) * d + rot, weight_floats = (size_t)(nq + nkv) * d * 2 + (size_t)nkv * dv;
+    // Many tokens: a block takes eight of them and fetches the biases and norm weights (as many bytes as two or three
+    // tokens' rows) once for all; few tokens: a block each, for the shortest step.
+    int tpb = T >= 2048 ? 8 : 1;
+    if ((row_floats + weight_floats) * sizeof(float) > 200 * 1024) tpb = 1;
+    const size_t smem = (row_floats + (tpb > 1 ? weight_floats : 0)) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     const int threads = (nq + nkv) * d >= 1024 ? 256 : 128;
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)v_first |
@@ -416,10 +474,10 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
             if (e != cudaSuccess) return (int)e; \
             configured[which] = smem; \
         } \
-        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT>, T, threads, smem, stream, (const TT*)qkv, bias, \
-                                      q_norm, k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, (const TT*)v_first, \
-                                      v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, page_size, num_pages, \
-                                      store_kv, vec4, status); \
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT>, (T + tpb - 1) / tpb, threads, smem, stream, \
+                                      (const TT*)qkv, bias, q_norm, k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
+                                      (const TT*)v_first, v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, \
+                                      page_size, num_pages, store_kv, vec4, tpb, status); \
     } while (0)
     if (dtype == DT_F32) PREP_CASE(float, 0);
     PREP_CASE(__nv_bfloat16, 1);

@@ -117,12 +117,13 @@ def test_norm_after_the_sum_leaves_the_next_input_in_decode_steps(rts):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("nq,nkv,d,dv,rot", [(4, 2, 48, 32, 48), (6, 2, 24, 16, 8), (4, 4, 16, 32, 16), (2, 1, 64, 64, 32), (3, 1, 40, 40, 0)])
-def test_attention_rows_are_prepared(rts, dtype, nq, nkv, d, dv, rot):
+@pytest.mark.parametrize("entries", [[(0, 5), (13, 3), (40, 1)], [(3, 2100), (0, 7)]])  # thousands of rows: several a block
+@pytest.mark.parametrize("nq,nkv,d,dv,rot", [(4, 2, 48, 32, 48), (6, 2, 24, 16, 8), (4, 4, 16, 32, 16), (2, 1, 64, 64, 32), (3, 1, 40, 40, 0),
+                                             (2, 2, 18, 10, 6)])  # the last: sizes that are no multiples of 4
+def test_attention_rows_are_prepared(rts, dtype, entries, nq, nkv, d, dv, rot):
     rt = rts[dtype]
     g = torch.Generator().manual_seed(d + dv)
     page, dp = 8, -(-max(d, dv) // 16) * 16
-    entries = [(0, 5), (13, 3), (40, 1)]
     tables, num_pages = _tables(entries, page)
     ctx, _ = K.make_context(rt, entries, page, tables)
     T, NQ, NK, NV = ctx.T, nq * d, nkv * d, nkv * dv
