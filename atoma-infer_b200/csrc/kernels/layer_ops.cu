@@ -134,7 +134,7 @@ extern "C" int short_conv_save(const float* x, float* state, const int* meta, co
 //  * conv_w / conv_state / conv_out: the sublayer after this norm reads the new rows through its own short
 //    convolution; for decode steps (every entry one row, so every earlier row comes from the state) this kernel
 //    also leaves that sublayer's input, new row + conv(new row, state), in conv_out.
-template <typename TD, typename TO>
+template <typename TD, typename TO, bool CONV>
 __global__ void __launch_bounds__(256)
 scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, float alpha, const float* __restrict__ w,
                           float eps, const int* __restrict__ meta, int H, float* __restrict__ keep, int keep_rows,
@@ -142,7 +142,8 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
                           const int* __restrict__ positions, const int* __restrict__ token_entry,
                           const int* __restrict__ cu_tokens, const int* __restrict__ slots,
                           const float* __restrict__ conv_w, const float* __restrict__ conv_state, int conv_taps,
-                          TO* __restrict__ conv_out, int vec4) {
+                          TO* __restrict__ conv_out_arg, int vec4) {
+    TO* const conv_out = CONV ? conv_out_arg : nullptr;  // the plain instantiation keeps its registers
     __shared__ float red[33];
     extern __shared__ __align__(16) float row[];  // H floats, and H more with conv_out
     pdl_wait();
@@ -243,18 +244,21 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
     const int threads = H >= 1024 ? 256 : 128;
     const size_t smem = (size_t)H * sizeof(float) * (conv_out ? 2 : 1);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    static size_t configured[4] = {0, 0, 0, 0};  // per instantiation; grows only, and is not set inside a capture again
+    static size_t configured[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per instantiation; grows only, and is not set inside a capture again
     if (keep_taps <= 1) keep = nullptr;
     const int vec4 = H % 4 == 0 && keep_stride % 4 == 0 && conv_stride % 4 == 0 &&
                      (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)keep | (uintptr_t)conv_w |
                        (uintptr_t)conv_state | (uintptr_t)conv_out) & 15) == 0;
 #define POSTNORM_CASE(TD, TO, which) \
+    if (conv_out) { POSTNORM_CASE2(TD, TO, true, 2 * which); } \
+    POSTNORM_CASE2(TD, TO, false, 2 * which + 1)
+#define POSTNORM_CASE2(TD, TO, CONV, which) \
     if (smem > 48 * 1024 && smem > configured[which]) { \
-        cudaError_t e = cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e = cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<TD, TO, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e; \
         configured[which] = smem; \
     } \
-    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, scaled_add_rmsnorm_kernel<TD, TO>, n, threads, smem, stream, resid, \
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, scaled_add_rmsnorm_kernel<TD, TO, CONV>, n, threads, smem, stream, resid, \
                                   (const TD*)delta, alpha, w, eps, meta, H, keep, keep_taps - 1, keep_stride, conv_stride, positions, token_entry, \
                                   cu_tokens, slots, conv_w, conv_state, conv_taps, (TO*)conv_out, vec4)
     if (delta_dtype == DT_F32 && conv_out_dtype == DT_F32) { POSTNORM_CASE(float, float, 0); }
@@ -262,6 +266,7 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
     else if (conv_out_dtype == DT_F32) { POSTNORM_CASE(__nv_bfloat16, float, 2); }
     else { POSTNORM_CASE(__nv_bfloat16, __nv_bfloat16, 3); }
 #undef POSTNORM_CASE
+#undef POSTNORM_CASE2
 }
 
 // ----------------------------------------------------------------------------- attention rows
@@ -282,48 +287,22 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
                    const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
                    const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
                    T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
-                   int store_kv, int vec4, int tokens_per_block, int* __restrict__ status) {
-    // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token; with several tokens a block also the
-    // biases and the norm weights, fetched once for all of them
+                   int store_kv, int vec4, int* __restrict__ status) {
+    // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
     extern __shared__ __align__(16) float vals[];
     __shared__ float red[66];
     pdl_wait();
     pdl_launch_dependents();
-    const int num_tokens = meta[META_NUM_TOKENS];
-    const int t_begin = blockIdx.x * tokens_per_block, t_end = min(t_begin + tokens_per_block, num_tokens);
-    if (t_begin >= t_end) return;
+    const int t = blockIdx.x;
+    if (t >= meta[META_NUM_TOKENS]) return;
     const int NQ = nq * d, NK = nkv * d, NV = nkv * dv, half = rot / 2;
     float* trig = vals + NQ + NK;
     const float *bias = bias_g, *q_norm = q_norm_g, *k_norm = k_norm_g;
-    if (tokens_per_block > 1) {
-        float* sb = trig + rot;
-        float* sq = sb + (NQ + NK + NV);
-        float* sk = sq + NQ;
-        for (int i = threadIdx.x; i < NQ + NK + NV; i += blockDim.x) {
-            if (bias_g) sb[i] = bias_g[i];
-            if (i < NQ && q_norm_g) sq[i] = q_norm_g[i];
-            if (i < NK && k_norm_g) sk[i] = k_norm_g[i];
-        }
-        if (bias_g) bias = sb;
-        if (q_norm_g) q_norm = sq;
-        if (k_norm_g) k_norm = sk;
-    }
     const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
     const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
-    for (int t = t_begin; t < t_end; ++t) {
-        __syncthreads();  // the staged weights are written; the token before is done with vals and trig
+    {
         const T* row = qkv + (size_t)t * (NQ + NK + NV);
         const int pos = positions[t];
-        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
-        int page = 0;
-        if (store_kv) {
-            const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
-            page = bt[pos / page_size];
-            if (page <= 0 || page >= num_pages) {
-                if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
-                page = 0;  // keys and values are dropped; the queries are still prepared
-            }
-        }
         float sq = 0.f, sk = 0.f;
         if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
             for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
@@ -342,6 +321,17 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
                 const float v = to_float(row[i]) + (bias ? bias[i] : 0.f);
                 vals[i] = v;
                 if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+            }
+        }
+        // after the row's loads are on their way: the token's cosines and sines, and its page
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
+        int page = 0;
+        if (store_kv) {
+            const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
+            page = bt[pos / page_size];
+            if (page <= 0 || page >= num_pages) {
+                if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+                page = 0;  // keys and values are dropped; the queries are still prepared
             }
         }
         float inv_q = 1.f, inv_k = 1.f;
@@ -409,7 +399,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
                 }
                 if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
             }
-            continue;
+            return;
         }
         // q and k: one item per (head, dim below dp); pairs of the rotated part are computed twice, once per half
         for (int it = threadIdx.x; it < heads * dp; it += blockDim.x) {
@@ -454,12 +444,7 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
                            int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages, int store_kv, int* status,
                            cudaStream_t stream) {
     if (T <= 0) return 0;
-    const size_t row_floats = (size_t)(nq + nkv) * d + rot, weight_floats = (size_t)(nq + nkv) * d * 2 + (size_t)nkv * dv;
-    // Many tokens: a block takes eight of them and fetches the biases and norm weights (as many bytes as two or three
-    // tokens' rows) once for all; few tokens: a block each, for the shortest step.
-    int tpb = T >= 2048 ? 8 : 1;
-    if ((row_floats + weight_floats) * sizeof(float) > 200 * 1024) tpb = 1;
-    const size_t smem = (row_floats + (tpb > 1 ? weight_floats : 0)) * sizeof(float);
+    const size_t smem = ((size_t)(nq + nkv) * d + rot) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     const int threads = (nq + nkv) * d >= 1024 ? 256 : 128;
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)v_first |
@@ -474,10 +459,10 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
             if (e != cudaSuccess) return (int)e; \
             configured[which] = smem; \
         } \
-        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT>, (T + tpb - 1) / tpb, threads, smem, stream, \
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT>, T, threads, smem, stream, \
                                       (const TT*)qkv, bias, q_norm, k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
                                       (const TT*)v_first, v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, \
-                                      page_size, num_pages, store_kv, vec4, tpb, status); \
+                                      page_size, num_pages, store_kv, vec4, status); \
     } while (0)
     if (dtype == DT_F32) PREP_CASE(float, 0);
     PREP_CASE(__nv_bfloat16, 1);
@@ -487,12 +472,14 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
 // ----------------------------------------------------------------------------- polynomial activation of normalised powers
 // out[t] = a N(z) + b N(z^2) + c N(z^3) + e with N(u) = u / sqrt(mean(u^2) + eps) over the row; powers element by
 // element; coef = (a, b, c, e).  The three mean squares are sums of z^2, z^4 and z^6, taken in one pass.
-template <typename T>
+template <typename T, int PER_THREAD>
 __global__ void __launch_bounds__(1024)
 polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps, T* __restrict__ out,
-                const int* __restrict__ meta, int F, int vec4) {
+                const int* __restrict__ meta, int F, int wide) {
     __shared__ float red[99];
-    constexpr int MAXC = 8;  // up to 8 x 4 values a thread stay in registers between the two passes
+    // Up to PER_THREAD (16 or 32) values a thread stay in registers between the two passes, as they were loaded (16
+    // bytes a load: a bfloat16 row costs half the registers of a float32 one, which lets more warps share a multiprocessor).
+    constexpr int VEC = 16 / sizeof(T), MAXC = PER_THREAD / VEC;
     const float a = coef[0], b = coef[1], c = coef[2], e0 = coef[3];
     pdl_wait();
     pdl_launch_dependents();
@@ -501,20 +488,25 @@ polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float e
     const T* zr = z + (size_t)t * F;
     T* o = out + (size_t)t * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-    const bool in_regs = vec4 && F <= 4 * MAXC * (int)blockDim.x;
-    float v[MAXC][4];
+    const bool in_regs = wide && F <= VEC * MAXC * (int)blockDim.x;
+    uint4 raw[MAXC];
     if (in_regs) {
 #pragma unroll
         for (int j = 0; j < MAXC; ++j) {
-            const int i = (threadIdx.x + j * blockDim.x) * 4;
-            if (i < F) {
-                load4(zr + i, v[j]);
+            const int i = (threadIdx.x + j * blockDim.x) * VEC;
+            if (i < F) raw[j] = *reinterpret_cast<const uint4*>(zr + i);
+        }
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float v2 = v[j][k] * v[j][k], v3 = v2 * v[j][k];
-                    s2 += v2;
-                    s4 = fmaf(v2, v2, s4);
-                    s6 = fmaf(v3, v3, s6);
+        for (int j = 0; j < MAXC; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * VEC;
+            if (i < F) {
+                const T* e = reinterpret_cast<const T*>(&raw[j]);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const float x = to_float(e[k]), x2 = x * x, x3 = x2 * x;
+                    s2 += x2;
+                    s4 = fmaf(x2, x2, s4);
+                    s6 = fmaf(x3, x3, s6);
                 }
             }
         }
@@ -531,17 +523,23 @@ polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float e
     const float n1 = a * rsqrtf(sums[0] / (float)F + eps), n2 = b * rsqrtf(sums[1] / (float)F + eps),
                 n3 = c * rsqrtf(sums[2] / (float)F + eps);
     if (in_regs) {
+        // the values are unpacked again from what was loaded: held unpacked since the first pass they would cost twice
+        // the registers (the empty statement keeps the compiler from doing just that)
+#pragma unroll
+        for (int j = 0; j < MAXC; ++j) asm volatile("" : "+r"(raw[j].x), "+r"(raw[j].y), "+r"(raw[j].z), "+r"(raw[j].w));
 #pragma unroll
         for (int j = 0; j < MAXC; ++j) {
-            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            const int i = (threadIdx.x + j * blockDim.x) * VEC;
             if (i < F) {
-                float r[4];
+                const T* e = reinterpret_cast<const T*>(&raw[j]);
+                uint4 res;
+                T* r = reinterpret_cast<T*>(&res);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float x = v[j][k], x2 = x * x;
-                    r[k] = n1 * x + n2 * x2 + n3 * (x2 * x) + e0;
+                for (int k = 0; k < VEC; ++k) {
+                    const float x = to_float(e[k]), x2 = x * x;
+                    r[k] = from_float<T>(n1 * x + n2 * x2 + n3 * (x2 * x) + e0);
                 }
-                store4(o + i, r);
+                *reinterpret_cast<uint4*>(o + i) = res;
             }
         }
         return;
@@ -555,13 +553,21 @@ polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float e
 extern "C" int polynorm(const void* z, int dtype, const float* coef, float eps, void* out, const int* meta, int T, int F,
                         cudaStream_t stream) {
     if (T <= 0) return 0;
-    const int vec4 = F % 4 == 0 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0;
-    // as many threads as keep a row in registers (32 values each), 128 at least and 1024 at most
-    int threads = ((F + 31) / 32 + 31) / 32 * 32;
+    // rows of whole 16-byte pieces that start on 16 bytes
+    const int wide = F % (dtype == DT_F32 ? 4 : 8) == 0 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0;
+    // as many threads as keep a row in registers, 16 values each (32 for rows beyond 16,384 values), 128 at least and
+    // 1024 at most
+    const int per = F <= 16 * 1024 ? 16 : 32;
+    int threads = ((F + per - 1) / per + 31) / 32 * 32;
     threads = threads < 128 ? 128 : threads > 1024 ? 1024 : threads;
-    if (dtype == DT_F32)
-        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, polynorm_kernel<float>, T, threads, 0, stream, (const float*)z, coef, eps,
-                                      (float*)out, meta, F, vec4);
-    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, polynorm_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)z,
-                                  coef, eps, (__nv_bfloat16*)out, meta, F, vec4);
+#define POLY_CASE(TT, PER) \
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, polynorm_kernel<TT, PER>, T, threads, 0, stream, (const TT*)z, coef, eps, \
+                                  (TT*)out, meta, F, wide)
+    if (dtype == DT_F32) {
+        if (per == 16) POLY_CASE(float, 16);
+        POLY_CASE(float, 32);
+    }
+    if (per == 16) POLY_CASE(__nv_bfloat16, 16);
+    POLY_CASE(__nv_bfloat16, 32);
+#undef POLY_CASE
 }
