@@ -279,10 +279,10 @@ extern "C" int scaled_add_rmsnorm(float* resid, const void* delta, int delta_dty
 //    nkv * dv); with v_out: the layer's values (biases added) are left there for later layers;
 //  * q goes to q_out [T, nq, dp], k and v to the token's slot of its page, heads of dp elements (dp >= d, dv;
 //    the tail is zeros, so that kernels that use one head size for keys and values can read them).
-template <typename T>
+template <typename T, typename TP>
 __global__ void __launch_bounds__(256)
-qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, const float* __restrict__ q_norm_g,
-                   const float* __restrict__ k_norm_g, float eps, const int* __restrict__ positions,
+qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, const TP* __restrict__ q_norm_g,
+                   const TP* __restrict__ k_norm_g, float eps, const int* __restrict__ positions,
                    const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
                    const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
                    const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
@@ -297,7 +297,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
     if (t >= meta[META_NUM_TOKENS]) return;
     const int NQ = nq * d, NK = nkv * d, NV = nkv * dv, half = rot / 2;
     float* trig = vals + NQ + NK;
-    const float *bias = bias_g, *q_norm = q_norm_g, *k_norm = k_norm_g;
+    const TP *bias = bias_g, *q_norm = q_norm_g, *k_norm = k_norm_g;
     const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
     const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
     {
@@ -318,7 +318,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
             }
         } else {
             for (int i = threadIdx.x; i < NQ + NK; i += blockDim.x) {
-                const float v = to_float(row[i]) + (bias ? bias[i] : 0.f);
+                const float v = to_float(row[i]) + (bias ? to_float(bias[i]) : 0.f);
                 vals[i] = v;
                 if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
             }
@@ -356,7 +356,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
                 T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
                 const int base = h * d, nb = is_q ? base : base - NQ;  // k heads follow the q heads in vals
                 const float inv = is_q ? inv_q : inv_k;
-                const float* nw = is_q ? q_norm : k_norm;
+                const TP* nw = is_q ? q_norm : k_norm;
                 auto normed4 = [&](int j, float (&o)[4]) {
                     float wv[4] = {1.f, 1.f, 1.f, 1.f};
                     load4(vals + base + j, o);
@@ -410,9 +410,9 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
             if (i < d) {
                 const int base = h * d;
                 const float inv = is_q ? inv_q : inv_k;
-                const float* nw = is_q ? q_norm : k_norm;
+                const TP* nw = is_q ? q_norm : k_norm;
                 const int nb = is_q ? base : base - NQ;
-                auto normed = [&](int j) { return vals[base + j] * inv * (nw ? nw[nb + j] : 1.f); };
+                auto normed = [&](int j) { return vals[base + j] * inv * (nw ? to_float(nw[nb + j]) : 1.f); };
                 if (i < rot) {
                     const int f = i < half ? i : i - half;
                     float lo, hi;
@@ -429,7 +429,7 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
             float r = 0.f;
             if (i < dv) {
                 const int j = h * dv + i;
-                r = to_float(row[NQ + NK + j]) + (bias ? bias[NQ + NK + j] : 0.f);
+                r = to_float(row[NQ + NK + j]) + (bias ? to_float(bias[NQ + NK + j]) : 0.f);
                 if (v_out) v_out[(size_t)t * NV + j] = from_float<T>(r);
                 if (v_first) r = (1.f - lam) * r + lam * to_float(v_first[(size_t)t * NV + j]);
             }
@@ -438,7 +438,9 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const float* __restrict__ bias_g, 
     }
 }
 
-extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const float* q_norm, const float* k_norm, float eps,
+// param_dtype: the type of bias, q_norm and k_norm (bfloat16 weights of a checkpoint may stay as they are stored: the
+// kernel widens them, exactly, as it reads them, and a token's row then brings half as many weight bytes with it)
+extern "C" int qkv_prepare(const void* qkv, int dtype, const void* bias, const void* q_norm, const void* k_norm, int param_dtype, float eps,
                            const int* positions, const int* token_entry, const int* meta, int group, const float* inv_freq,
                            int rot, const void* v_first, const float* v_lambda, void* v_out, void* q_out, void* cache, int T,
                            int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages, int store_kv, int* status,
@@ -451,21 +453,23 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const float* bias, const 
                           (uintptr_t)v_out | (uintptr_t)q_out | (uintptr_t)cache;
     const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % 8 == 0 && (all & 15) == 0;
     cudaError_t e;
-    static size_t configured[2] = {0, 0};  // the attribute only ever grows (and is not set inside a capture again)
-#define PREP_CASE(TT, which) \
+    static size_t configured[3] = {0, 0, 0};  // the attribute only ever grows (and is not set inside a capture again)
+#define PREP_CASE(TT, TP, which) \
     do { \
         if (smem > 48 * 1024 && smem > configured[which]) { \
-            e = cudaFuncSetAttribute(qkv_prepare_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            e = cudaFuncSetAttribute(qkv_prepare_kernel<TT, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
             configured[which] = smem; \
         } \
-        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT>, T, threads, smem, stream, \
-                                      (const TT*)qkv, bias, q_norm, k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_kernel<TT, TP>, T, threads, smem, stream, \
+                                      (const TT*)qkv, (const TP*)bias, (const TP*)q_norm, (const TP*)k_norm, eps, positions, token_entry, meta, group, inv_freq, rot, \
                                       (const TT*)v_first, v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, nkv, d, dv, dp, \
                                       page_size, num_pages, store_kv, vec4, status); \
     } while (0)
-    if (dtype == DT_F32) PREP_CASE(float, 0);
-    PREP_CASE(__nv_bfloat16, 1);
+    if (dtype == DT_F32 && param_dtype != DT_F32) return (int)cudaErrorInvalidValue;
+    if (dtype == DT_F32) PREP_CASE(float, float, 0);
+    if (param_dtype == DT_F32) PREP_CASE(__nv_bfloat16, float, 1);
+    PREP_CASE(__nv_bfloat16, __nv_bfloat16, 2);
 #undef PREP_CASE
 }
 

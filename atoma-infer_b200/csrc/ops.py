@@ -386,8 +386,13 @@ class CudaOps:
         """Rows [q | k | v] of the fused projection become attention's inputs: biases, root-mean-square norms over
         the whole q and the whole k part (weights ``q_norm`` / ``k_norm``), rotation of the first ``rot`` dims of
         every head, v <- (1 - lambda) v + lambda v_first; q to ``q_out`` [T, nq * dp], k and v to the pages as heads of
-        dp elements (zeros behind d and dv).  ``v_out``: the values (biases added, unmixed) for later layers."""
-        self._check(self.lib.qkv_prepare(_p(qkv), _code(qkv), _p(bias), _p(q_norm), _p(k_norm), ctypes.c_float(eps),
+        dp elements (zeros behind d and dv).  ``v_out``: the values (biases added, unmixed) for later layers.
+        ``bias``, ``q_norm`` and ``k_norm`` share one type, float32 or (beside bfloat16 rows) bfloat16."""
+        params = [t for t in (bias, q_norm, k_norm) if t is not None]
+        if len({t.dtype for t in params}) > 1:
+            raise KernelError("biases and norm weights of the attention rows must share one type")
+        pcode = _code(params[0]) if params else DT_F32
+        self._check(self.lib.qkv_prepare(_p(qkv), _code(qkv), _p(bias), _p(q_norm), _p(k_norm), pcode, ctypes.c_float(eps),
                                          _p(ctx.positions), _p(ctx.token_entry), _p(ctx.meta), max(group, 0), _p(inv_freq),
                                          int(rot) if inv_freq is not None else 0, _p(v_first), _p(v_lambda), _p(v_out),
                                          _p(q_out), _p(cache_layer), ctx.T, nq, nkv, d, dv, dp, page_size, num_pages,

@@ -115,8 +115,13 @@ class Attention(Mixer):
         if not self.prepared:
             return
         f32 = lambda name: tensors[pre + n[name]].to(torch.float32).contiguous()  # noqa: E731  (exact widening)
-        self.b_qkv = torch.cat([f32("q_bias"), f32("k_bias"), f32("v_bias")]).contiguous() if self.bias else None
-        self.w_q_norm, self.w_k_norm = (f32("q_norm"), f32("k_norm")) if self.qk_norm is not None else (None, None)
+        # Biases and norm weights stay as the loader left them when that is one type for all (bfloat16 from a bfloat16
+        # checkpoint: the kernel widens them, exactly, as it reads them); else all are widened here.
+        names = (["q_bias", "k_bias", "v_bias"] if self.bias else []) + (["q_norm", "k_norm"] if self.qk_norm is not None else [])
+        same = len({tensors[pre + n[x]].dtype for x in names}) <= 1
+        get = (lambda name: tensors[pre + n[name]].contiguous()) if same else f32  # noqa: E731
+        self.b_qkv = torch.cat([get("q_bias"), get("k_bias"), get("v_bias")]).contiguous() if self.bias else None
+        self.w_q_norm, self.w_k_norm = (get("q_norm"), get("k_norm")) if self.qk_norm is not None else (None, None)
         self.v_lambda = f32("v_mix").reshape(1) if self.v_mix is not None else None
         if self.padded_dim != self.v_head_dim:  # the attention's output has heads of the padded size: zero columns for the tail
             w = self.w_o.new_zeros((self.hidden, self.num_heads, self.padded_dim))

@@ -361,7 +361,7 @@ def design_kernels(rt, hbm, median_ms) -> None:
         qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(bf)
         cache = torch.zeros(num_pages, 2, nkv, PAGE, d, device=dev, dtype=bf)
         q_out = torch.empty(T, nq * d, device=dev, dtype=bf)
-        bias, qn, kn = (torch.ones(n, device=dev) for n in ((nq + 2 * nkv) * d, nq * d, nkv * d))
+        bias, qn, kn = (torch.ones(n, device=dev, dtype=bf) for n in ((nq + 2 * nkv) * d, nq * d, nkv * d))
         inv_freq = torch.ones(d // 2, device=dev)
         v_first, lam = torch.randn(T, nkv * d, device=dev).to(bf), torch.tensor([0.3], device=dev)
         z, gu = torch.randn(T, I, device=dev).to(bf), torch.randn(T, 2 * I, device=dev).to(bf)

@@ -133,6 +133,7 @@ class HostOps:
         n = int(meta[META_NUM_TOKENS])
         off, stride = int(meta[META_BT_OFFSET + group]), int(meta[META_BT_STRIDE + group])
         NQ, NK = nq * d, nkv * d
+        bias, q_norm, k_norm = (t.float() if t is not None else None for t in (bias, q_norm, k_norm))
         rows = qkv[:n].float() + (bias if bias is not None else 0)
         q, k, v = rows[:, :NQ], rows[:, NQ:NQ + NK], rows[:, NQ + NK:]
         if q_norm is not None:
