@@ -348,56 +348,71 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
         T* vpage = kpage + kv_block;
         const int heads = nq + (page > 0 ? nkv : 0);
         if (vec4) {
-            // q and k: one item per (head, four dims); an item of the rotated part's first half also makes its partner
-            const int upd = dp / 4;
-            for (int it = threadIdx.x; it < heads * upd; it += blockDim.x) {
-                const int h = it / upd, i = (it % upd) * 4;
-                const bool is_q = h < nq;
-                T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
-                const int base = h * d, nb = is_q ? base : base - NQ;  // k heads follow the q heads in vals
-                const float inv = is_q ? inv_q : inv_k;
-                const TP* nw = is_q ? q_norm : k_norm;
-                auto normed4 = [&](int j, float (&o)[4]) {
-                    float wv[4] = {1.f, 1.f, 1.f, 1.f};
-                    load4(vals + base + j, o);
-                    if (nw) load4(nw + nb + j, wv);
+            // q and k: one item per (head, four dims); an item of the rotated part's first half also makes its partner, so a
+            // head has dp / 4 - half / 4 items.  Head and item of a thread move on by additions (no division in the loop).
+            const int upd = dp / 4, hq = half / 4, uh = upd - hq;
+            {
+                int h = threadIdx.x / uh, u = threadIdx.x % uh;
+                const int dh = blockDim.x / uh, du = blockDim.x % uh;
+                while (h < heads) {
+                    const int i = u < hq ? 4 * u : 4 * u + half;
+                    const bool is_q = h < nq;
+                    T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
+                    const int base = h * d, nb = is_q ? base : base - NQ;  // k heads follow the q heads in vals
+                    const float inv = is_q ? inv_q : inv_k;
+                    const TP* nw = is_q ? q_norm : k_norm;
+                    auto normed4 = [&](int j, float (&o)[4]) {
+                        float wv[4] = {1.f, 1.f, 1.f, 1.f};
+                        load4(vals + base + j, o);
+                        if (nw) load4(nw + nb + j, wv);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) o[k] = o[k] * inv * wv[k];
-                };
-                float r[4] = {0.f, 0.f, 0.f, 0.f};
-                if (i < half) {
-                    float u[4], w2[4], hi[4];
-                    normed4(i, u);
-                    normed4(i + half, w2);
+                        for (int k = 0; k < 4; ++k) o[k] = o[k] * inv * wv[k];
+                    };
+                    float r[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (u < hq) {
+                        float a[4], b[4], hi[4], cs[4], sn[4];
+                        normed4(i, a);
+                        normed4(i + half, b);
+                        load4(trig + i, cs);
+                        load4(trig + half + i, sn);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) rotate_pair(u[k], w2[k], trig[i + k], trig[half + i + k], r[k], hi[k]);
-                    store4(dst + i + half, hi);
-                } else if (i < rot) {
-                    continue;  // written by its partner
-                } else if (i < d) {
-                    normed4(i, r);
-                }
-                store4(dst + i, r);
-            }
-            for (int it = threadIdx.x; it < nkv * upd; it += blockDim.x) {
-                const int h = it / upd, i = (it % upd) * 4;
-                float r[4] = {0.f, 0.f, 0.f, 0.f};
-                if (i < dv) {
-                    const int j = h * dv + i;
-                    float bv[4] = {0.f, 0.f, 0.f, 0.f};
-                    load4(row + NQ + NK + j, r);
-                    if (bias) load4(bias + NQ + NK + j, bv);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) r[k] += bv[k];
-                    if (v_out) store4(v_out + (size_t)t * NV + j, r);
-                    if (v_first) {
-                        float f[4];
-                        load4(v_first + (size_t)t * NV + j, f);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) r[k] = (1.f - lam) * r[k] + lam * f[k];
+                        for (int k = 0; k < 4; ++k) rotate_pair(a[k], b[k], cs[k], sn[k], r[k], hi[k]);
+                        store4(dst + i + half, hi);
+                    } else if (i < d) {
+                        normed4(i, r);
                     }
+                    store4(dst + i, r);
+                    u += du;
+                    h += dh;
+                    if (u >= uh) { u -= uh; ++h; }
                 }
-                if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
+            }
+            if (page > 0 || v_out) {
+                int h = threadIdx.x / upd, u = threadIdx.x % upd;
+                const int dh = blockDim.x / upd, du = blockDim.x % upd;
+                while (h < nkv) {
+                    const int i = 4 * u;
+                    float r[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (i < dv) {
+                        const int j = h * dv + i;
+                        float bv[4] = {0.f, 0.f, 0.f, 0.f};
+                        load4(row + NQ + NK + j, r);
+                        if (bias) load4(bias + NQ + NK + j, bv);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) r[k] += bv[k];
+                        if (v_out) store4(v_out + (size_t)t * NV + j, r);
+                        if (v_first) {
+                            float f[4];
+                            load4(v_first + (size_t)t * NV + j, f);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) r[k] = (1.f - lam) * r[k] + lam * f[k];
+                        }
+                    }
+                    if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
+                    u += du;
+                    h += dh;
+                    if (u >= upd) { u -= upd; ++h; }
+                }
             }
             return;
         }
