@@ -398,6 +398,16 @@ class CudaOps:
                                          _p(q_out), _p(cache_layer), ctx.T, nq, nkv, d, dv, dp, page_size, num_pages,
                                          int(store_kv), _p(self.status), self._stream()), "qkv_prepare")
 
+    def narrow(self, x, dtype):
+        """Float32 rows in the compute type (rounded once); the same tensor if it has that type already."""
+        if x.dtype == dtype:
+            return x
+        if x.dtype != torch.float32 or dtype != torch.bfloat16:
+            raise KernelError(f"narrow: float32 to bfloat16 only, got {x.dtype} to {dtype}")
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        self._check(self.lib.cast_f32_bf16(_p(x), _p(out), ctypes.c_size_t(x.numel()), self._stream()), "cast_f32_bf16")
+        return out
+
     def polynorm(self, z, coef, eps: float, out, meta):
         """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(u) = u / sqrt(mean(u^2) + eps); coef = (a, b, c, e)."""
         self._check(self.lib.polynorm(_p(z), _code(z), _p(coef), ctypes.c_float(eps), _p(out), _p(meta), z.shape[0],

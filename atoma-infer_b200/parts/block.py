@@ -166,7 +166,8 @@ class PostNormBlock(Block):
         return None
 
     def _plain_input(self, resid):
-        return resid if resid.dtype == self.rt.dtype else resid.to(self.rt.dtype)
+        """Without a filter a sublayer reads the stream itself, in the compute type."""
+        return self.rt.ops.narrow(resid, self.rt.dtype)
 
 
 register_part("block", "postnorm", PostNormBlock)

@@ -162,6 +162,10 @@ class HostOps:
                 cache[page, 0, :, p % page_size, :d] = k[t].to(cache.dtype)
                 cache[page, 1, :, p % page_size, :dv] = v[t].reshape(nkv, dv).to(cache.dtype)
 
+    def narrow(self, x, dtype):
+        self._count()
+        return x.to(dtype)
+
     def polynorm(self, z, coef, eps, out, meta):
         self._count()
         n = int(meta[META_NUM_TOKENS])
