@@ -453,152 +453,6 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
     }
 }
 
-// The same with the row in registers instead of shared memory, for sizes that are multiples of 4 (16-byte accesses) and
-// rows of at most MAXU * blockDim items: an item is four dims of a head and, in the first half of the rotated part, the
-// four dims they rotate with; a thread loads its items once, adds the biases and takes its share of the two sums of
-// squares, and after the block's sums it scales, rotates and stores what it holds.  Only the token's cosines and sines
-// pass through shared memory.
-template <typename T, typename TP, int MAXU>
-__global__ void __launch_bounds__(1024)
-qkv_prepare_regs_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias, const TP* __restrict__ q_norm,
-                        const TP* __restrict__ k_norm, float eps, const int* __restrict__ positions,
-                        const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
-                        const float* __restrict__ inv_freq, int rot, const T* __restrict__ v_first,
-                        const float* __restrict__ v_lambda, T* __restrict__ v_out, T* __restrict__ q_out,
-                        T* __restrict__ cache, int nq, int nkv, int d, int dv, int dp, int page_size, int num_pages,
-                        int store_kv, int* __restrict__ status) {
-    extern __shared__ __align__(16) float trig[];  // cos[rot / 2], sin[rot / 2] of the token
-    __shared__ float red[66];
-    pdl_wait();
-    pdl_launch_dependents();
-    const int t = blockIdx.x;
-    if (t >= meta[META_NUM_TOKENS]) return;
-    const int NQ = nq * d, NK = nkv * d, NV = nkv * dv, half = rot / 2;
-    const int upd = dp / 4, hq = half / 4, uh = upd - hq, heads_all = nq + nkv;
-    const T* row = qkv + (size_t)t * (NQ + NK + NV);
-    const int pos = positions[t];
-    const int h0 = threadIdx.x / uh, u0 = threadIdx.x % uh, dh = blockDim.x / uh, du = blockDim.x % uh;
-    float a[MAXU][4], b[MAXU][4];
-    float sq = 0.f, sk = 0.f;
-    {
-        int h = h0, u = u0;
-#pragma unroll
-        for (int n = 0; n < MAXU; ++n) {
-            if (h < heads_all) {
-                const int i = u < hq ? 4 * u : 4 * u + half, at = h * d + i;  // k heads follow the q heads in the row
-                float part = 0.f;
-                if (i < d) {
-                    float bv[4] = {0.f, 0.f, 0.f, 0.f};
-                    load4(row + at, a[n]);
-                    if (bias) load4(bias + at, bv);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) { a[n][k] += bv[k]; part = fmaf(a[n][k], a[n][k], part); }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) a[n][k] = 0.f;
-                }
-                if (u < hq) {
-                    float bv[4] = {0.f, 0.f, 0.f, 0.f};
-                    load4(row + at + half, b[n]);
-                    if (bias) load4(bias + at + half, bv);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) { b[n][k] += bv[k]; part = fmaf(b[n][k], b[n][k], part); }
-                }
-                if (h < nq) sq += part; else sk += part;
-            }
-            u += du;
-            h += dh;
-            if (u >= uh) { u -= uh; ++h; }
-        }
-    }
-    // after the row's loads are on their way: the token's cosines and sines, and its page
-    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
-    int page = 0;
-    if (store_kv) {
-        const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
-        page = bt[pos / page_size];
-        if (page <= 0 || page >= num_pages) {
-            if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
-            page = 0;  // keys and values are dropped; the queries are still prepared
-        }
-    }
-    float inv_q = 1.f, inv_k = 1.f;
-    if (q_norm || k_norm) {  // (its barriers also publish the cosines and sines)
-        float both[2] = {sq, sk};
-        block_sums<2>(both, red);
-        if (q_norm) inv_q = rsqrtf(both[0] / (float)NQ + eps);
-        if (k_norm) inv_k = rsqrtf(both[1] / (float)NK + eps);
-    } else {
-        __syncthreads();
-    }
-    const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
-    const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
-    T* kpage = cache + (size_t)page * 2 * kv_block + (size_t)(pos % page_size) * dp;
-    T* vpage = kpage + kv_block;
-    {
-        int h = h0, u = u0;
-#pragma unroll
-        for (int n = 0; n < MAXU; ++n) {
-            const bool is_q = h < nq;
-            if (h < heads_all && (is_q || page > 0)) {
-                const int i = u < hq ? 4 * u : 4 * u + half;
-                T* dst = is_q ? q_out + ((size_t)t * nq + h) * dp : kpage + (size_t)(h - nq) * head_block;
-                const float inv = is_q ? inv_q : inv_k;
-                const TP* nw = is_q ? q_norm : k_norm;
-                const int nb = (is_q ? h : h - nq) * d + i;
-                if (i < d) {
-                    float wv[4] = {1.f, 1.f, 1.f, 1.f};
-                    if (nw) load4(nw + nb, wv);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) a[n][k] = a[n][k] * inv * wv[k];
-                }
-                if (u < hq) {
-                    float wv[4] = {1.f, 1.f, 1.f, 1.f}, cs[4], sn[4], lo[4], hi[4];
-                    if (nw) load4(nw + nb + half, wv);
-                    load4(trig + i, cs);
-                    load4(trig + half + i, sn);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) rotate_pair(a[n][k], b[n][k] * inv * wv[k], cs[k], sn[k], lo[k], hi[k]);
-                    store4(dst + i, lo);
-                    store4(dst + i + half, hi);
-                } else {
-                    store4(dst + i, a[n]);
-                }
-            }
-            u += du;
-            h += dh;
-            if (u >= uh) { u -= uh; ++h; }
-        }
-    }
-    if (page > 0 || v_out) {
-        int h = threadIdx.x / upd, u = threadIdx.x % upd;
-        const int vdh = blockDim.x / upd, vdu = blockDim.x % upd;
-        while (h < nkv) {
-            const int i = 4 * u;
-            float r[4] = {0.f, 0.f, 0.f, 0.f};
-            if (i < dv) {
-                const int j = h * dv + i;
-                float bv[4] = {0.f, 0.f, 0.f, 0.f};
-                load4(row + NQ + NK + j, r);
-                if (bias) load4(bias + NQ + NK + j, bv);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) r[k] += bv[k];
-                if (v_out) store4(v_out + (size_t)t * NV + j, r);
-                if (v_first) {
-                    float f[4];
-                    load4(v_first + (size_t)t * NV + j, f);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) r[k] = (1.f - lam) * r[k] + lam * f[k];
-                }
-            }
-            if (page > 0) store4(vpage + (size_t)h * head_block + i, r);
-            u += vdu;
-            h += vdh;
-            if (u >= upd) { u -= upd; ++h; }
-        }
-    }
-}
-
 // param_dtype: the type of bias, q_norm and k_norm (bfloat16 weights of a checkpoint may stay as they are stored: the
 // kernel widens them, exactly, as it reads them, and a token's row then brings half as many weight bytes with it)
 extern "C" int qkv_prepare(const void* qkv, int dtype, const void* bias, const void* q_norm, const void* k_norm, int param_dtype, float eps,
@@ -615,25 +469,6 @@ extern "C" int qkv_prepare(const void* qkv, int dtype, const void* bias, const v
     const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)v_first |
                           (uintptr_t)v_out | (uintptr_t)q_out | (uintptr_t)cache;
     const int vec4 = d % 4 == 0 && dv % 4 == 0 && dp % 4 == 0 && rot % 8 == 0 && (all & 15) == 0;
-    // The row in registers (four items a thread at most) where the sizes allow it
-    constexpr int MAXU = 4;
-    const int items = vec4 ? (nq + nkv) * (dp / 4 - rot / 8) : 0;
-    if (vec4 && items <= MAXU * 1024 && (size_t)rot * sizeof(float) <= 48 * 1024) {
-        int need = ((items + MAXU - 1) / MAXU + 31) / 32 * 32;
-        const int least = T < 512 ? 256 : 128;  // few tokens: the shortest path through a token; many: more blocks a multiprocessor
-        const int rthreads = need < least ? least : need;
-        const size_t rsmem = (size_t)rot * sizeof(float);
-#define PREP_REGS(TT, TP) \
-    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, qkv_prepare_regs_kernel<TT, TP, MAXU>, T, rthreads, rsmem, stream, \
-                                  (const TT*)qkv, (const TP*)bias, (const TP*)q_norm, (const TP*)k_norm, eps, positions, token_entry, \
-                                  meta, group, inv_freq, rot, (const TT*)v_first, v_lambda, (TT*)v_out, (TT*)q_out, (TT*)cache, nq, \
-                                  nkv, d, dv, dp, page_size, num_pages, store_kv, status)
-        if (dtype == DT_F32 && param_dtype != DT_F32) return (int)cudaErrorInvalidValue;
-        if (dtype == DT_F32) PREP_REGS(float, float);
-        if (param_dtype == DT_F32) PREP_REGS(__nv_bfloat16, float);
-        PREP_REGS(__nv_bfloat16, __nv_bfloat16);
-#undef PREP_REGS
-    }
     cudaError_t e;
     static size_t configured[3] = {0, 0, 0};  // the attribute only ever grows (and is not set inside a capture again)
 #define PREP_CASE(TT, TP, which) \
