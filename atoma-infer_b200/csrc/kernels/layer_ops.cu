@@ -45,12 +45,14 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
                   TO* __restrict__ y, const int* __restrict__ meta, const int* __restrict__ positions,
                   const int* __restrict__ token_entry, const int* __restrict__ cu_tokens,
                   const int* __restrict__ slots, int C, int taps, int add_input, long long slot_stride, int vec4) {
+    // The step's metadata is written by no kernel of the step: it is read before the wait, while the kernel ahead ends.
+    const int t = blockIdx.x;
+    const bool live = t < meta[META_NUM_TOKENS];
+    const int e = live ? token_entry[t] : 0, p = live ? positions[t] : 0, first = live ? cu_tokens[e] : 0, R = taps - 1;
+    const float* st = state + (size_t)(live ? slots[e] : 0) * slot_stride;
     pdl_wait();  // like the norm kernel: the kernels behind start once this one's wait is over
     pdl_launch_dependents();
-    const int t = blockIdx.x;
-    if (t >= meta[META_NUM_TOKENS]) return;
-    const int e = token_entry[t], p = positions[t], first = cu_tokens[e], R = taps - 1;
-    const float* st = state + (size_t)slots[e] * slot_stride;
+    if (!live) return;
     if (vec4) {  // four channels a thread, 16-byte accesses (C a multiple of 4, buffers on 16 bytes)
         for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -146,21 +148,24 @@ scaled_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delt
     TO* const conv_out = CONV ? conv_out_arg : nullptr;  // the plain instantiation keeps its registers
     __shared__ float red[33];
     extern __shared__ __align__(16) float row[];  // H floats, and H more with conv_out
+    // The step's metadata is written by no kernel of the step: it is read before the wait, while the kernel ahead ends.
+    const int t = blockIdx.x;
+    const bool live = t < meta[META_NUM_TOKENS];
+    const int e = live && (keep || conv_out) ? token_entry[t] : 0;
+    const int slot = live && (keep || conv_out) ? slots[e] : 0, my_pos = live && (keep || conv_out) ? positions[t] : 0;
+    float* kept = nullptr;
+    if (live && keep && keeps_row(t, e, cu_tokens, keep_rows))
+        kept = keep + (size_t)slot * keep_stride + (size_t)(my_pos % keep_rows) * H;
     pdl_wait();
     pdl_launch_dependents();
-    const int t = blockIdx.x;
-    if (t >= meta[META_NUM_TOKENS]) return;
+    if (!live) return;
     float* x = resid + (size_t)t * H;
     const TD* dl = delta ? delta + (size_t)t * H : nullptr;
-    const int e = (keep || conv_out) ? token_entry[t] : 0;
-    float* kept = nullptr;
-    if (keep && keeps_row(t, e, cu_tokens, keep_rows))
-        kept = keep + (size_t)slots[e] * keep_stride + (size_t)(positions[t] % keep_rows) * H;
     // The part of the next sublayer's convolution that comes from its state does not depend on this norm: it is taken
     // in the first pass, with the loads of the row, and waits in shared memory behind the row.
     const int R = conv_taps - 1;
-    const int p = conv_out ? positions[t] : 0;
-    const float* st = conv_out ? conv_state + (size_t)slots[e] * conv_stride : nullptr;
+    const int p = my_pos;
+    const float* st = conv_out ? conv_state + (size_t)slot * conv_stride : nullptr;
     float* pre = row + H;
     float ss = 0.f;
     if (vec4) {  // four values a thread, 16-byte accesses; the sum's order differs from the scalar form's, but is as fixed
@@ -291,18 +296,31 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
     // the q and k parts of the row, then cos[rot / 2], sin[rot / 2] of the token
     extern __shared__ __align__(16) float vals[];
     __shared__ float red[66];
-    pdl_wait();
-    pdl_launch_dependents();
+    // What depends on the step's metadata and on constants alone comes before the wait, while the kernel ahead ends: the
+    // token's position, its cosines and sines, its page.
     const int t = blockIdx.x;
-    if (t >= meta[META_NUM_TOKENS]) return;
+    const bool live = t < meta[META_NUM_TOKENS];
     const int NQ = nq * d, NK = nkv * d, NV = nkv * dv, half = rot / 2;
     float* trig = vals + NQ + NK;
+    const int pos = live ? positions[t] : 0;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
+    int page = 0;
+    if (live && store_kv) {
+        const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
+        page = bt[pos / page_size];
+        if (page <= 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+            page = 0;  // keys and values are dropped; the queries are still prepared
+        }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!live) return;
     const TP *bias = bias_g, *q_norm = q_norm_g, *k_norm = k_norm_g;
     const float lam = (v_first && v_lambda) ? *v_lambda : 0.f;
     const size_t head_block = (size_t)page_size * dp, kv_block = (size_t)nkv * head_block;
     {
         const T* row = qkv + (size_t)t * (NQ + NK + NV);
-        const int pos = positions[t];
         float sq = 0.f, sk = 0.f;
         if (vec4) {  // four values a thread (d, dv, dp and rot / 2 multiples of 4, buffers on 16 bytes)
             for (int i = threadIdx.x * 4; i < NQ + NK; i += blockDim.x * 4) {
@@ -321,17 +339,6 @@ qkv_prepare_kernel(const T* __restrict__ qkv, const TP* __restrict__ bias_g, con
                 const float v = to_float(row[i]) + (bias ? to_float(bias[i]) : 0.f);
                 vals[i] = v;
                 if (i < NQ) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
-            }
-        }
-        // after the row's loads are on their way: the token's cosines and sines, and its page
-        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
-        int page = 0;
-        if (store_kv) {
-            const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
-            page = bt[pos / page_size];
-            if (page <= 0 || page >= num_pages) {
-                if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
-                page = 0;  // keys and values are dropped; the queries are still prepared
             }
         }
         float inv_q = 1.f, inv_k = 1.f;
@@ -502,10 +509,11 @@ polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float e
     // bytes a load: a bfloat16 row costs half the registers of a float32 one, which lets more warps share a multiprocessor).
     constexpr int VEC = 16 / sizeof(T), MAXC = PER_THREAD / VEC;
     const float a = coef[0], b = coef[1], c = coef[2], e0 = coef[3];
+    const int t = blockIdx.x;
+    const bool live = !meta || t < meta[META_NUM_TOKENS];  // (metadata and coefficients: read before the wait)
     pdl_wait();
     pdl_launch_dependents();
-    const int t = blockIdx.x;
-    if (meta && t >= meta[META_NUM_TOKENS]) return;
+    if (!live) return;
     const T* zr = z + (size_t)t * F;
     T* o = out + (size_t)t * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
