@@ -81,6 +81,30 @@ class StepContext:
         return self.meta[off:off + self.S * stride].view(self.S, stride)
 
 
+@dataclass
+class PendingSum:
+    """An addition to the residual stream that is still to be made: mult * (sum of ``terms``) + ``rows`` + ``vector``.
+    ``terms`` are a block's sublayer outputs [T, H] in the compute dtype (at most two), ``rows`` float32 [T, H],
+    ``vector`` float32 [H] (the same for every token).  The norm that follows (``Norm.forward``) takes the sum in
+    float32, term by term in this order, in the pass in which it also norms the updated row; a block that has no
+    norm for it calls ``apply_pending``."""
+
+    terms: Sequence[torch.Tensor] = ()
+    mult: float = 1.0
+    rows: Optional[torch.Tensor] = None
+    vector: Optional[torch.Tensor] = None
+
+
+def apply_pending(ops, resid: torch.Tensor, delta, ctx: "StepContext") -> None:
+    """Adds what a block left pending (a tensor or a ``PendingSum``; None: nothing) into the float32 stream."""
+    if delta is None:
+        return
+    if isinstance(delta, PendingSum):
+        ops.sum_rmsnorm(resid, delta, None, 0.0, None, ctx.meta, ctx.T)
+    else:
+        resid.add_(delta)
+
+
 class Part:
     """Base of all parts: parameters from the spec, tensors by checkpoint name."""
 
@@ -206,8 +230,8 @@ class Block(Part):
 
     ``forward(resid, delta, ctx, cache)``: ``resid`` is the float32 residual stream
     [T, H], ``delta`` what the previous block left to be added (None at the first);
-    returns this block's own pending addition.  Keeping the last addition pending lets
-    the next norm do it, in float32, in the same pass.  ``ctx.shared["next_run"]`` holds
+    returns this block's own pending addition (a tensor, or a ``PendingSum`` of several terms and a
+    factor).  Keeping the last addition pending lets the next norm do it, in float32, in the same pass.  ``ctx.shared["next_run"]`` holds
     (block, cache view) of the layer run that follows, or None: a block whose last kernel can
     also leave that block's input may do so under ``ctx.shared["prepared_input"]`` =
     (that block, tensor), which the next block takes if it finds itself named."""

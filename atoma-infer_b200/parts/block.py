@@ -17,7 +17,7 @@ from typing import Optional
 
 import torch
 
-from .base import Block
+from .base import Block, PendingSum, apply_pending
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm",
                   "feed_forward": "mlp"}
@@ -120,9 +120,8 @@ class PostNormBlock(Block):
         return state[:, at:at + n] if state is not None and n else None
 
     def forward(self, resid, delta, ctx, cache):
-        if delta is not None:  # a block before this one left its addition pending
-            resid.add_(delta)
         ops = self.rt.ops
+        apply_pending(ops, resid, delta, ctx)  # a block before this one left its addition pending
         mixer_cache = cache
         if self.mixer.state_bytes() != self.state_bytes() and cache.state is not None:
             from dataclasses import replace
@@ -171,3 +170,46 @@ class PostNormBlock(Block):
 
 
 register_part("block", "postnorm", PostNormBlock)
+
+
+class ParallelBlock(Block):
+    """x <- x + mult * (mixer(h) + ff(h)) with h = norm1(x): one norm, both sublayers read its output.  The sum is
+    left pending as a ``PendingSum`` (both terms, the factor), which the next norm adds into the float32 stream term
+    by term.  Parameters: ``norm``, ``mixer``, ``feed_forward`` (None: the mixer alone), ``mult``, ``names``."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        names = {"norm1": "norm1", "mixer": "mix", "feed_forward": "mlp", **(params.get("names") or {})}
+        mk = lambda fam, spec, name: part_class(fam, spec["kind"])(spec, f"{prefix}.{name}")  # noqa: E731
+        self.mult = float(params.get("mult", 1.0))
+        self.norm1 = mk("norm", params["norm"], names["norm1"])
+        self.mixer = mk("mixer", params["mixer"], names["mixer"])
+        ff = params.get("feed_forward")
+        self.feed_forward = mk("feed_forward", ff, names["feed_forward"]) if ff else None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.feed_forward) if p is not None]
+
+    def streamed_weights(self):
+        return self.mixer.streamed_weights() + (self.feed_forward.streamed_weights() if self.feed_forward else [])
+
+    def activation_width(self):
+        return max(p.activation_width() for p in self.parts())
+
+    def declare(self):
+        return [d for p in self.parts() for d in p.declare()]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        for p in self.parts():
+            p.bind(tensors, rt)
+
+    def forward(self, resid, delta, ctx, cache):
+        h = self.norm1.forward(resid, delta, ctx)
+        a = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return PendingSum((a,), self.mult)
+        return PendingSum((a, self.feed_forward.forward(h, ctx)), self.mult)
+
+
+register_part("block", "parallel", ParallelBlock)

@@ -135,8 +135,8 @@ def plan_stacks(blocks, runs, run_owner, run_group, rt) -> Dict[int, DecodeStack
         fusions, j = [here[0]], i + 1
         while j < len(runs):
             nxt = describe(j)
-            if nxt is None or nxt[1:] != here[1:]:
-                break
+            if nxt is None or nxt[1:] != here[1:] or getattr(runs[j], "before", None) is not None:
+                break  # (a run before which the stream receives something starts a stretch of its own)
             fusions.append(nxt[0])
             j += 1
         stacks[i] = DecodeStack(i, fusions, here[2], rt)

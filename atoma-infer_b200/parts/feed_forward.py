@@ -92,3 +92,45 @@ class PolyNormFF(FeedForward):
 
 
 register_part("feed_forward", "polynorm", PolyNormFF)
+
+
+class DenseActFF(FeedForward):
+    """Dense feed-forward with an elementwise activation: down(act(up(x))), no biases.
+
+    Parameters: ``hidden``, ``intermediate``, ``activation`` (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715
+    z^3)))), ``names`` (suffixes of up and down; default ``.up``, ``.down``).
+    """
+
+    ACTIVATIONS = ("gelu_tanh",)
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.activation = str(params.get("activation", "gelu_tanh"))
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not known (known: {self.ACTIVATIONS})")
+        names = {"up": ".up", "down": ".down", **(params.get("names") or {})}
+        self.t_up, self.t_down = prefix + names["up"], prefix + names["down"]
+
+    def activation_width(self):
+        return self.intermediate
+
+    def declare(self):
+        return [TensorDecl(self.t_up, (self.intermediate, self.hidden)), TensorDecl(self.t_down, (self.hidden, self.intermediate))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_up, self.w_down = tensors[self.t_up].contiguous(), tensors[self.t_down].contiguous()
+
+    def streamed_weights(self):
+        return [self.w_up, self.w_down]
+
+    def forward(self, x, ctx):
+        ops = self.rt.ops
+        z = ops.linear(x, self.w_up, meta=ctx.meta)
+        act = torch.empty_like(z)
+        ops.activation(z, act, self.activation, ctx.meta)
+        return ops.linear(act, self.w_down, meta=ctx.meta)
+
+
+register_part("feed_forward", "dense_act", DenseActFF)

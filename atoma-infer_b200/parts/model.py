@@ -18,11 +18,11 @@ import torch
 from ..cache.spec import CacheGroup, CacheNeed
 from ..config.registry import part_class
 from ..weights.loader import TensorDecl
-from .base import LayerCache, Runtime, StepContext
+from .base import LayerCache, PendingSum, Runtime, StepContext, apply_pending
 from .decode_stack import MAX_ROWS as STACK_MAX_ROWS, plan_stacks
 
 # the registrations of the built-in parts
-from . import attention, block, embedding, feed_forward, filter, head, norm, position  # noqa: F401
+from . import attention, block, embedding, feed_forward, filter, head, latent_attention, moe, norm, position, ssm  # noqa: F401
 
 
 @dataclass
@@ -31,10 +31,21 @@ class LayerSpec:
     block: Dict[str, Any]    # {"kind": "prenorm", "norm": {...}, "mixer": {...}, "feed_forward": {...}}
 
 
+@dataclass(frozen=True)
+class StreamAdd:
+    """What the stream receives right before a run: the embedding output (the stream as it was before the first
+    layer) and/or row ``row`` of the learned table ``table`` (a name in ``ModelSpec.stream_tables``)."""
+
+    embedding: bool = False
+    table: Optional[str] = None
+    row: int = 0
+
+
 @dataclass
 class LayerRun:
     layer: int                       # index into ModelSpec.layers
     cache_of: Optional[int] = None   # layer whose cache this run uses (None: its own)
+    before: Optional[StreamAdd] = None
 
 
 @dataclass
@@ -51,6 +62,7 @@ class ModelSpec:
     embedding: Optional[Dict[str, Any]] = None
     head: Optional[Dict[str, Any]] = None
     schedule: Optional[List[LayerRun]] = None       # None: every layer once, in order
+    stream_tables: Dict[str, Tuple[int, int]] = field(default_factory=dict)  # checkpoint name -> [rows, hidden], see StreamAdd
     ignored_tensors: Tuple[str, ...] = ()           # globs a checkpoint may carry unused
     max_position: int = 0
     eos_token_ids: Tuple[int, ...] = ()
@@ -83,6 +95,7 @@ def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
     for blk in _build_layers(spec):
         decls += blk.declare()
     decls += part_class("norm", spec.final_norm["kind"])(spec.final_norm, spec.final_norm_prefix).declare()
+    decls += [TensorDecl(name, tuple(shape)) for name, shape in spec.stream_tables.items()]
     return decls + head.declare()
 
 
@@ -129,6 +142,11 @@ class DecoderModel:
                 gi = len(self.groups) - 1
             self.run_group[i] = (gi, len(self.groups[gi].layers))
             self.groups[gi].layers.append(i)
+        for r in self.runs:
+            if r.before is not None and r.before.table is not None and r.before.table not in spec.stream_tables:
+                raise ValueError(f"schedule adds a row of {r.before.table!r}, which is no stream table of the model")
+        self.keeps_embedding = any(r.before is not None and r.before.embedding for r in self.runs)
+        self.watch = None  # callable(run index, stream, pending addition) after every run that goes block by block: a test aid
         # fixed-size state per request, for every run of a mixer that has some
         self.state_bytes = [self.blocks[r.layer].state_bytes() for r in self.runs]
         # a step of this model can be captured in a CUDA graph if no part reads the host-side entry list
@@ -139,10 +157,13 @@ class DecoderModel:
         decls = self.embedding.declare()
         for blk in self.blocks:
             decls += blk.declare()
+        decls += [TensorDecl(name, tuple(shape)) for name, shape in self.spec.stream_tables.items()]
         return decls + self.final_norm.declare() + self.head.declare()
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
+        # tables whose rows are added to the float32 stream: widened exactly
+        self.stream_tables = {name: tensors[name].to(torch.float32).contiguous() for name in self.spec.stream_tables}
         self.embedding.bind(tensors, rt)
         for blk in self.blocks:
             blk.bind(tensors, rt)
@@ -160,6 +181,7 @@ class DecoderModel:
         at the flat-batch rows listed in ``rows`` (a device int32 array)."""
         resid = self.embedding.forward(ctx)
         delta = None
+        first = resid.clone() if self.keeps_embedding else None  # the embedding output, for runs that add it again
         view_of = lambda k: cache.layer_view(self.run_owner[k], writes=self.runs[k].cache_of is None, state_run=k)  # noqa: E731
         # decode steps of few rows: stretches of layers as one launch (off by default), or as a chain of streamed linears
         # with the norms folded into them
@@ -168,6 +190,18 @@ class DecoderModel:
         i = 0
         while i < len(self.runs):
             stack = stacks.get(i)
+            add = self.runs[i].before
+            if add is not None:  # joins what is pending: the run's first norm takes it all in one pass
+                if not isinstance(delta, PendingSum):
+                    delta = PendingSum((delta,) if delta is not None else ())
+                if delta.rows is not None or delta.vector is not None:
+                    apply_pending(self.rt.ops, resid, delta, ctx)
+                    delta = PendingSum()
+                delta = PendingSum(delta.terms, delta.mult, first if add.embedding else None,
+                                   self.stream_tables[add.table][add.row] if add.table is not None else None)
+            if stack is not None and isinstance(delta, PendingSum):
+                apply_pending(self.rt.ops, resid, delta, ctx)
+                delta = None
             if stack is not None and one_launch and stack.supports(ctx.T):
                 stack.forward(resid, delta, ctx, [view_of(k) for k in range(stack.first, stack.end)])
                 delta, i = None, stack.end
@@ -179,6 +213,8 @@ class DecoderModel:
             # what runs next, for a block whose last kernel can also leave the next block's input (see Block.forward)
             ctx.shared["next_run"] = (self.blocks[self.runs[i + 1].layer], view_of(i + 1)) if i + 1 < len(self.runs) else None
             delta = self.blocks[self.runs[i].layer].forward(resid, delta, ctx, view_of(i))
+            if self.watch is not None:
+                self.watch(i, resid, delta)
             i += 1
         if num_rows == 0:
             join = getattr(self.rt.ops, "join_side_work", None)

@@ -15,7 +15,7 @@ import torch
 
 from ..config.registry import register_part
 from ..weights.loader import TensorDecl
-from .base import Norm
+from .base import Norm, PendingSum
 
 
 class RMSNorm(Norm):
@@ -40,7 +40,10 @@ class RMSNorm(Norm):
     def forward(self, resid, delta, ctx, rows=None, num_rows=0):
         n = num_rows if rows is not None else ctx.T
         out = torch.empty((n, self.size), dtype=self.rt.dtype, device=resid.device)
-        self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, ctx.meta, n, rows=rows)
+        if isinstance(delta, PendingSum):  # several terms, a factor, rows and a vector: one pass all the same
+            self.rt.ops.sum_rmsnorm(resid, delta, self.weight, self.eps, out, ctx.meta, n, rows=rows)
+        else:
+            self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, ctx.meta, n, rows=rows)
         return out
 
     def fused(self):

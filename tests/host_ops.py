@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 import plain_dosovik as PD
+import plain_tutezen as PT
 import plain_llama as P
 from atoma_infer_b200.csrc.ops import (META_BT_OFFSET, META_BT_STRIDE, META_NUM_ROWS, META_NUM_TOKENS, STATUS_WORDS,
                                        CudaOps)
@@ -190,8 +191,147 @@ class HostOps:
             g = nq // nkv
             for h in range(nq):
                 sc = (k[:, h // g] @ qq[h]) * scale
-                w = torch.softmax(torch.cat([sc, sc.new_zeros(1)]), 0)[:-1] if sink else torch.softmax(sc, 0)
+                if torch.is_tensor(sink):  # a learned sink per head: exp(sink_h) in the denominator
+                    w = torch.softmax(torch.cat([sc, sink[h].float().reshape(1)]), 0)[:-1]
+                else:
+                    w = torch.softmax(torch.cat([sc, sc.new_zeros(1)]), 0)[:-1] if sink else torch.softmax(sc, 0)
                 out[t, h * d:(h + 1) * d] = (w @ v[:, h // g]).to(out.dtype)
+
+    # -- parallel blocks, state-space mixers, latent attention, routed experts
+    def sum_rmsnorm(self, resid, pending, w, eps, out, meta, n, rows=None):
+        self._count()
+        if rows is None:
+            n = int(meta[META_NUM_TOKENS])
+            idx = torch.arange(n)
+        else:
+            n = int(meta[META_NUM_ROWS])
+            idx = rows[:n].long()
+        x = resid[idx]
+        if pending is not None:
+            add = torch.zeros_like(x)
+            for t in pending.terms:
+                add = add + t[idx].float()
+            x = x + pending.mult * add
+            if pending.rows is not None:
+                x = x + pending.rows[idx]
+            if pending.vector is not None:
+                x = x + pending.vector
+        if rows is None:
+            resid[:n] = x
+        if out is not None:
+            out[:n] = P.rms_norm(x, w, eps).to(out.dtype)
+
+    def causal_conv_act(self, u, w, bias, state, ctx, out, *, act="silu"):
+        self._count()
+        taps, wt = w.shape[0], w.t()  # the kernels take [taps, channels]
+        for _, a, b, slot in self._entries(ctx):
+            p0 = int(ctx.positions[a])
+            past = [state[slot, p % (taps - 1)] if p >= 0 else torch.zeros_like(state[slot, 0]) for p in range(p0 - taps + 1, p0)]
+            rows = torch.cat([torch.stack(past), u[a:b].float()]) if past else u[a:b].float()
+            y = PT.causal_conv(rows, wt.float(), bias if bias is not None else torch.zeros(wt.shape[0]))[len(past):]
+            out[a:b] = (PT.silu(y) if act == "silu" else y).to(out.dtype)
+
+    def causal_conv_save(self, u, state, ctx, taps):
+        self._count()
+        for _, a, b, slot in self._entries(ctx):
+            for t in range(max(a, b - (taps - 1)), b):
+                state[slot, int(ctx.positions[t]) % (taps - 1)] = u[t].float()
+
+    def ssm_scan(self, xbc, dt, dt_bias, a_log, d_skip, state, ctx, y, *, heads, head_dim, nstate, groups):
+        self._count()
+        inner, per = heads * head_dim, heads // groups
+        for _, a, b, slot in self._entries(ctx):
+            for t in range(a, b):
+                row = xbc[t].float()
+                x = row[:inner].view(heads, head_dim)
+                B = row[inner:inner + groups * nstate].view(groups, nstate)
+                C = row[inner + groups * nstate:].view(groups, nstate)
+                step = PT.softplus(dt[t].float() + dt_bias)
+                for h in range(heads):
+                    S = torch.exp(-torch.exp(a_log[h]) * step[h]) * state[slot, h] + step[h] * torch.outer(B[h // per], x[h])
+                    state[slot, h] = S
+                    y[t, h * head_dim:(h + 1) * head_dim] = S.T @ C[h // per] + d_skip[h] * x[h]
+
+    def gated_group_norm(self, y, z, w, groups, eps, out, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        out[:n] = (PT.grouped_rms(y[:n] * PT.silu(z[:n].float()), groups, eps) * w).to(out.dtype)
+
+    def rms_rows(self, x, w, eps, out, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        out[:n] = (PT.rms_divide(x[:n].float(), eps) * w).to(out.dtype)
+
+    def head_linear(self, x, w, out, meta, gate=None):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        y = torch.einsum("thk,hnk->thn", x[:n].float(), w.float())
+        if gate is not None:
+            y = y * torch.sigmoid(gate[:n].float())
+        out[:n] = y.to(out.dtype)
+
+    def latent_rows(self, q_rot, q_abs, dkv, norm_w, eps, ctx, cache, group, q_out, *, heads, kv_rank, rot_dim, padded,
+                    page_size, num_pages, store, inv_freq=None, rotary_dims=0):
+        self._count()
+        meta = ctx.meta
+        n = int(meta[META_NUM_TOKENS])
+        off, stride = int(meta[META_BT_OFFSET + group]), int(meta[META_BT_STRIDE + group])
+        pos = ctx.positions[:n]
+
+        def turn(v):  # pairs (2i, 2i+1) of the first rotary_dims dimensions
+            if not rotary_dims:
+                return v
+            ang = pos.float()[:, None] * inv_freq
+            while ang.dim() < v.dim():
+                ang = ang.unsqueeze(1)
+            cs, sn = torch.cos(ang), torch.sin(ang)
+            o = v.clone()
+            a, b = v[..., 0:rotary_dims:2], v[..., 1:rotary_dims:2]
+            o[..., 0:rotary_dims:2] = a * cs - b * sn
+            o[..., 1:rotary_dims:2] = b * cs + a * sn
+            return o
+
+        c = PT.rms_divide(dkv[:n, :kv_rank].float(), eps) * norm_w
+        key = torch.cat([c, turn(dkv[:n, kv_rank:].float())], -1)
+        q_out[:n] = 0
+        qv = q_out[:n].view(n, heads, padded)
+        qv[..., :kv_rank] = q_abs[:n].to(q_out.dtype)
+        qv[..., kv_rank:kv_rank + rot_dim] = turn(q_rot[:n].float()).to(q_out.dtype)
+        if store:
+            for t in range(n):
+                p = int(pos[t])
+                page = int(meta[off + int(ctx.token_entry[t]) * stride + p // page_size])
+                if not 0 < page < num_pages:
+                    self.status[1] = t + 1
+                    continue
+                cache[page, :, 0, p % page_size] = 0
+                cache[page, :, 0, p % page_size, :kv_rank + rot_dim] = key[t].to(cache.dtype)
+
+    def activation(self, z, out, kind, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        out[:n] = {"gelu_tanh": PT.gelu_tanh}[kind](z[:n].float()).to(out.dtype)
+
+    def moe_route(self, h, w_router, ids, wts, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        idx, wt = PT.route(h[:n].float(), w_router, ids.shape[1])
+        ids[:n], wts[:n] = idx.to(torch.int32), wt
+
+    def moe_experts(self, h, ids, wts, w_gate_up, w_down, shared, out, meta):
+        self._count()
+        n = int(meta[META_NUM_TOKENS])
+        f = w_gate_up.shape[1] // 2
+        for t in range(n):
+            acc = torch.zeros(w_down.shape[1])
+            for k in range(ids.shape[1]):
+                e = int(ids[t, k])
+                gu = w_gate_up[e].float() @ h[t].float()
+                act = (PT.silu(gu[:f]) * gu[f:]).to(h.dtype).float()
+                acc = acc + wts[t, k] * (w_down[e].float() @ act)
+            if shared is not None:
+                acc = acc + shared[t].float()
+            out[t] = acc.to(out.dtype)
 
     def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None, slots=None):
         self._count()
