@@ -54,8 +54,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
                    const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
-                   int store_kv, int nq, int window, int chunk, int sink, float scale_log2, int num_pages, int splits,
-                   int cluster_merge, int* __restrict__ status) {
+                   int store_kv, int nq, int window, int chunk, int sink, const float* __restrict__ sink_values, float scale_log2,
+                   int num_pages, int splits, int cluster_merge, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // tiles start on 1024-byte boundaries: TMA writes them with the 128-byte swizzle, whose pattern follows the address
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -320,14 +320,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     __syncthreads();
     for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
         int r = idx / D, i = idx % D;
-        // the softmax's sink (a key of score 0 without a value) is one more partial result, of the first split
+        // the softmax's sink (a key without a value, of score 0 or of the head's learned score, which no scale touches)
+        // is one more partial result, of the first split
         const bool with_sink = sink && split == 0;
-        float mx = with_sink ? 0.f : -INFINITY;
+        const float sink_at = with_sink && sink_values ? sink_values[kvh * G + r] * LOG2E : 0.f;
+        float mx = with_sink ? sink_at : -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, mbuf[w * (32 + 16 * D) + r]);
         float lsum = 0.f, acc = 0.f;
         if (mx > -INFINITY) {
-            if (with_sink) lsum = fast_exp2(-mx);
+            if (with_sink) lsum = fast_exp2(sink_at - mx);
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) {
                 const float* p = mbuf + w * (32 + 16 * D);
@@ -474,7 +476,7 @@ __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                     const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, int chunk, int sink,
-                    float scale_log2, int num_pages, int bt_cap, int* __restrict__ status) {
+                    const float* __restrict__ sink_values, float scale_log2, int num_pages, int bt_cap, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* kv = qtile + PF_ROWS * LDS;
@@ -554,9 +556,14 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     float o[PF_MT][DTILES][4];
 #pragma unroll
     for (int mt = 0; mt < PF_MT; ++mt) {
-        // with a sink the softmax has one more key, of score 0 and without a value: the running maximum and sum start there
-        m[mt][0] = m[mt][1] = sink ? 0.f : -INFINITY;
-        l[mt][0] = l[mt][1] = sink ? 1.f : 0.f;
+        // with a sink the softmax has one more key, without a value and of score 0 or of the head's learned score
+        // (which no scale touches): the running maximum and sum start there
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int hd = (wrow + mt * 16 + (lane >> 2) + 8 * h) % G;
+            m[mt][h] = sink ? (sink_values ? sink_values[kvh * G + hd] * LOG2E : 0.f) : -INFINITY;
+            l[mt][h] = sink ? 1.f : 0.f;
+        }
 #pragma unroll
         for (int dt = 0; dt < DTILES; ++dt) o[mt][dt][0] = o[mt][dt][1] = o[mt][dt][2] = o[mt][dt][3] = 0.f;
     }
@@ -707,10 +714,11 @@ extern "C" int attn_decode_max_splits(int nq, int nkv) {
 
 // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0);
 // sink: one more term in the softmax's denominator, a key of score 0 without a value.
-extern "C" int attn_prefill_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                                   const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
-                                   int page_size, int num_pages, int window, int chunk, int sink, float scale, int max_context,
-                                   int* status, cudaStream_t stream) {
+// sink_values (one float per query head, or null): the sink's score per head instead of 0.
+extern "C" int attn_prefill_sinks(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                  const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                                  int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
+                                  float scale, int max_context, int* status, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
     if (nq % nkv || nq / nkv > 16) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
@@ -729,8 +737,16 @@ extern "C" int attn_prefill_masked(const void* q, int q_stride, const void* cach
         configured = smem;
     }
     return (int)launch_kernel(attn_prefill_kernel, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L, meta,
-                              group, cu_tokens, ctx_lens, (bf16*)out, nq, window, chunk, sink, scale * LOG2E, num_pages, bt_cap,
-                              status);
+                              group, cu_tokens, ctx_lens, (bf16*)out, nq, window, chunk, sink, sink_values, scale * LOG2E, num_pages,
+                              bt_cap, status);
+}
+
+extern "C" int attn_prefill_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                   const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
+                                   int page_size, int num_pages, int window, int chunk, int sink, float scale, int max_context,
+                                   int* status, cudaStream_t stream) {
+    return attn_prefill_sinks(q, q_stride, cache, meta, group, cu_tokens, ctx_lens, out, S, max_q_len, nq, nkv, page_size,
+                              num_pages, window, chunk, sink, nullptr, scale, max_context, status, stream);
 }
 
 extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, const int* meta, int group,
@@ -795,11 +811,12 @@ extern "C" int attn_decode_flat(const void* q, int q_stride, const void* cache, 
 // and neither scratch nor counters is touched.  Otherwise `scratch`: attn_decode_scratch_floats(...) floats when
 // splits > 1, and `counters`: S * nkv ints, zero before the first launch (the kernel leaves them zero).  `inv_freq` (rot/2 floats) switches the fused rotation on: q is
 // then the unrotated projection row and, with store_kv, the new key and value are written here too.
-extern "C" int attn_decode_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                                  const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
-                                  const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
-                                  int num_pages, int window, int chunk, int sink, float scale, int splits, int cluster_merge,
-                                  int max_context, int* status, cudaStream_t stream) {
+// sink_values (one float per query head, or null): the sink's score per head instead of 0.
+extern "C" int attn_decode_sinks(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                 const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                                 const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                                 int num_pages, int window, int chunk, int sink, const float* sink_values, float scale, int splits,
+                                 int cluster_merge, int max_context, int* status, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (nq % nkv || nq / nkv > 16 || splits < 1) return (int)cudaErrorInvalidValue;
     if (splits == 1) cluster_merge = 0;
@@ -869,7 +886,17 @@ extern "C" int attn_decode_masked(const void* q, int q_stride, const void* cache
     cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta, group,
                                    cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
-                                   window, chunk, sink, scale * LOG2E, num_pages, splits, cluster_merge, status);
+                                   window, chunk, sink, sink_values, scale * LOG2E, num_pages, splits, cluster_merge, status);
+}
+
+extern "C" int attn_decode_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                  const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                                  const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                                  int num_pages, int window, int chunk, int sink, float scale, int splits, int cluster_merge,
+                                  int max_context, int* status, cudaStream_t stream) {
+    return attn_decode_sinks(q, q_stride, cache, meta, group, cu_tokens, positions, out, scratch, counters, inv_freq, rot,
+                             store_kv, S, nq, nkv, page_size, num_pages, window, chunk, sink, nullptr, scale, splits, cluster_merge,
+                             max_context, status, stream);
 }
 
 extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const int* meta, int group,

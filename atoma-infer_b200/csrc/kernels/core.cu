@@ -415,12 +415,13 @@ extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const i
 // token came alone, in a portion of a prompt, or beside other requests.
 #define ATTN_KT 64
 #define ATTN_THREADS 128
+#define ATTN_ACC 4
 template <typename T>
 __global__ void __launch_bounds__(ATTN_THREADS)
 attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ token_entry,
                     const int* __restrict__ positions, T* __restrict__ out, int nq, int window, int chunk, int sink,
-                    float scale, int num_pages, int* __restrict__ status) {
+                    const float* __restrict__ sink_values, float scale, int num_pages, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
@@ -437,8 +438,9 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
     const int ld = d + 1;
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
     for (int i = tid; i < d; i += ATTN_THREADS) qs[i] = to_float(qrow[i]);
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
-    float acc[2] = {0.f, 0.f};  // head sizes up to 2 * ATTN_THREADS
+    // (a learned sink: the head's own score instead of 0, which no scale touches)
+    float m = sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
+    float acc[ATTN_ACC] = {};  // head sizes up to ATTN_ACC * ATTN_THREADS
     int kstart = window > 0 ? max(0, p - window + 1) : 0;
     if (chunk > 0) kstart = max(kstart, p - p % chunk);
     for (int k0 = kstart; k0 <= p; k0 += ATTN_KT) {
@@ -476,7 +478,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
         }
         __syncthreads();
 #pragma unroll
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < ATTN_ACC; ++a) {
             int i = tid + a * ATTN_THREADS;
             if (i < d) {
                 float o = acc[a] * corr;
@@ -488,18 +490,19 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
     T* orow = out + ((size_t)t * nq + h) * d;
     float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < ATTN_ACC; ++a) {
         int i = tid + a * ATTN_THREADS;
         if (i < d) orow[i] = from_float<T>(acc[a] * inv);
     }
 }
 
-extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
-                            const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
-                            int page_size, int num_pages, int window, int chunk, int sink, float scale, int* status,
-                            cudaStream_t stream) {
+// sink_values (one float per query head, or null): the sink's score per head instead of 0.
+extern "C" int attn_generic_sinks(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
+                                  const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
+                                  int page_size, int num_pages, int window, int chunk, int sink, const float* sink_values,
+                                  float scale, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (d > 2 * ATTN_THREADS) return (int)cudaErrorInvalidValue;
+    if (d > ATTN_ACC * ATTN_THREADS) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, d};
     size_t smem = (size_t)(d + ATTN_KT + 40 + ATTN_KT * (d + 1)) * sizeof(float);
     dim3 grid(T, nq);
@@ -514,7 +517,7 @@ extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int 
         }
         return (int)launch_kernel(attn_generic_kernel<float>, grid, ATTN_THREADS, smem, stream, (const float*)q, q_stride,
                                   (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq, window, chunk, sink,
-                                  scale, num_pages, status);
+                                  sink_values, scale, num_pages, status);
     } else {
         if (smem > configured_bf16) {
             e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -523,8 +526,16 @@ extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int 
         }
         return (int)launch_kernel(attn_generic_kernel<__nv_bfloat16>, grid, ATTN_THREADS, smem, stream,
                                   (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry,
-                                  positions, (__nv_bfloat16*)out, nq, window, chunk, sink, scale, num_pages, status);
+                                  positions, (__nv_bfloat16*)out, nq, window, chunk, sink, sink_values, scale, num_pages, status);
     }
+}
+
+extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
+                            const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
+                            int page_size, int num_pages, int window, int chunk, int sink, float scale, int* status,
+                            cudaStream_t stream) {
+    return attn_generic_sinks(q, q_stride, cache, dtype, meta, group, token_entry, positions, out, T, nq, nkv, d, page_size,
+                              num_pages, window, chunk, sink, nullptr, scale, status, stream);
 }
 
 // ----------------------------------------------------------------------------- SwiGLU gate

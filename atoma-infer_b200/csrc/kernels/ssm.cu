@@ -1,0 +1,333 @@
+// Kernels of a state-space mixer of the Mamba-2 kind: the short causal convolution with bias and activation in
+// front of the recurrence, the recurrence itself (sequential over a request's tokens, or cut into chunks of time that
+// run side by side), and the gated norm in equal parts behind it.  Storage is float32 or bfloat16; the recurrence,
+// its step sizes and decays, the gate and the norm are float32 always.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- causal convolution, bias, activation
+// y[t, c] = act(bias[c] + sum_j w[j, c] * u[t - taps + 1 + j, c]) over the rows of each request, zeros before its
+// start.  u is a slice of a wider row (u_stride elements from row to row); w is [taps, C].  Rows before the step's
+// portion come from the request's state: a ring of R = taps - 1 float32 rows per state slot (slot_stride floats from
+// one slot to the next), the row of position p at ring place p mod R.  The ring is written by causal_conv_save AFTER
+// this kernel has read it.  act 0: none; 1: SiLU.
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv_act_kernel(const T* __restrict__ u, long long u_stride, const float* __restrict__ w,
+                       const float* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
+                       T* __restrict__ y, const int* __restrict__ meta, const int* __restrict__ positions,
+                       const int* __restrict__ token_entry, const int* __restrict__ cu_tokens,
+                       const int* __restrict__ slots, int C, int taps, int act) {
+    // The step's metadata is written by no kernel of the step: it is read before the wait, while the kernel ahead ends.
+    const int t = blockIdx.x;
+    const bool live = t < meta[META_NUM_TOKENS];
+    const int e = live ? token_entry[t] : 0, p = live ? positions[t] : 0, first = live ? cu_tokens[e] : 0, R = taps - 1;
+    const float* st = state ? state + (size_t)(live ? slots[e] : 0) * slot_stride : nullptr;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!live) return;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = bias ? bias[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {  // oldest tap first: a fixed order
+            const int back = taps - 1 - j, src = p - back;
+            if (src < 0) continue;
+            const float v = (t - back >= first) ? to_float(u[(size_t)(t - back) * u_stride + c]) : st[(size_t)(src % R) * C + c];
+            acc = fmaf(w[(size_t)j * C + c], v, acc);
+        }
+        if (act == 1) acc = acc / (1.f + expf(-acc));
+        y[(size_t)t * C + c] = from_float<T>(acc);
+    }
+}
+
+extern "C" int causal_conv_act(const void* u, int dtype, long long u_stride, const float* w, const float* bias,
+                               const float* state, long long slot_stride, void* y, const int* meta, const int* positions,
+                               const int* token_entry, const int* cu_tokens, const int* slots, int T, int C, int taps,
+                               int act, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (taps < 1 || (taps > 1 && !state)) return (int)cudaErrorInvalidValue;
+    const int threads = C >= 1024 ? 256 : 128;
+    if (dtype == DT_F32)
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, causal_conv_act_kernel<float>, T, threads, 0, stream, (const float*)u,
+                                      u_stride, w, bias, state, slot_stride, (float*)y, meta, positions, token_entry, cu_tokens,
+                                      slots, C, taps, act);
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, causal_conv_act_kernel<__nv_bfloat16>, T, threads, 0, stream,
+                                  (const __nv_bfloat16*)u, u_stride, w, bias, state, slot_stride, (__nv_bfloat16*)y, meta,
+                                  positions, token_entry, cu_tokens, slots, C, taps, act);
+}
+
+// The last R rows of u of every entry go to its ring.
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv_save_kernel(const T* __restrict__ u, long long u_stride, float* __restrict__ state, long long slot_stride,
+                        const int* __restrict__ meta, const int* __restrict__ positions, const int* __restrict__ token_entry,
+                        const int* __restrict__ cu_tokens, const int* __restrict__ slots, int C, int R) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    const int e = token_entry[t];
+    if (t < cu_tokens[e + 1] - R) return;
+    float* st = state + (size_t)slots[e] * slot_stride + (size_t)(positions[t] % R) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) st[c] = to_float(u[(size_t)t * u_stride + c]);
+}
+
+extern "C" int causal_conv_save(const void* u, int dtype, long long u_stride, float* state, long long slot_stride,
+                                const int* meta, const int* positions, const int* token_entry, const int* cu_tokens,
+                                const int* slots, int T, int C, int taps, cudaStream_t stream) {
+    if (T <= 0 || taps <= 1) return 0;
+    const int threads = C >= 1024 ? 256 : 128;
+    if (dtype == DT_F32)
+        return (int)launch_kernel(causal_conv_save_kernel<float>, T, threads, 0, stream, (const float*)u, u_stride, state,
+                                  slot_stride, meta, positions, token_entry, cu_tokens, slots, C, taps - 1);
+    return (int)launch_kernel(causal_conv_save_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)u, u_stride,
+                              state, slot_stride, meta, positions, token_entry, cu_tokens, slots, C, taps - 1);
+}
+
+// ----------------------------------------------------------------------------- the recurrence
+// Per head h (of group h / (heads / groups)) a matrix S of N x P: S_t = exp(-exp(a_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T,
+// y_t = S_t^T C_t + d_h x_t, dt_t = softplus(raw_t + dt_bias_h).  Rows of `xbc` are [x: heads * P | B: groups * N |
+// C: groups * N]; `dt` is a slice of a wider row.
+//
+// One block per (head, entry[, chunk]).  Thread (p, r) keeps NPT rows n = r * NPT .. of column p in registers, R
+// threads share a column (R * NPT >= N; rows beyond N see B = C = 0 and stay zero).  Tokens come through shared
+// memory SCAN_TT at a time; y_t is summed over a thread's rows in order, then over the R threads by shuffles: an order
+// that depends on the sizes only.
+//
+// pass 0: the entry's tokens in order, from the state slot, y written, the slot updated.
+// Cut into chunks of `chunk_len` tokens (counted from the entry's first token in the step), three launches:
+// pass 1: chunk c < last runs from S = 0 and leaves its end state in scratch[c + 1] and its total decay in decay[c];
+// (ssm_chunk_states) scratch[0] = slot's state, scratch[c] = decay[c - 1] * scratch[c - 1] + scratch[c], in order;
+// pass 3: chunk c runs again from scratch[c] and writes y; the last chunk updates the slot.
+#define SCAN_TT 16
+
+template <typename T, int NPT>
+__global__ void __launch_bounds__(512)
+ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__ dt, long long dt_stride,
+                const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                float* __restrict__ state, long long slot_stride, float* __restrict__ y, const int* __restrict__ meta,
+                const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads, int P, int N, int groups, int R,
+                int pass, int chunk_len, int max_chunks, float* __restrict__ scratch, float* __restrict__ decay) {
+    extern __shared__ __align__(16) float sm[];
+    const int NP = R * NPT;                 // padded N
+    float* Bs = sm;                         // [SCAN_TT][NP]
+    float* Cs = Bs + SCAN_TT * NP;          // [SCAN_TT][NP]
+    float* xs = Cs + SCAN_TT * NP;          // [SCAN_TT][P]
+    float* dts = xs + SCAN_TT * P;          // [SCAN_TT]
+    float* decs = dts + SCAN_TT;            // [SCAN_TT]
+    const int h = blockIdx.x, e = blockIdx.y, c = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (e >= meta[META_NUM_ENTRIES]) return;
+    const int first = cu_tokens[e], count = cu_tokens[e + 1] - first;
+    const int nchunks = pass == 0 ? 1 : (count + chunk_len - 1) / chunk_len;
+    if (c >= nchunks || (pass == 1 && c == nchunks - 1)) return;
+    const int t0 = first + (pass == 0 ? 0 : c * chunk_len), t1 = pass == 0 ? first + count : min(first + count, t0 + chunk_len);
+    const int tid = threadIdx.x, p = tid / R, r = tid % R;
+    const bool real = p < P;
+    const int inner = heads * P, g = h / (heads / groups);
+    const float rate = expf(a_log[h]), bias = dt_bias[h], dskip = d_skip[h];
+    const size_t HS = (size_t)N * P;        // floats of one head's matrix
+    float* slot_state = state + (size_t)slots[e] * slot_stride + (size_t)h * HS;
+    float* chunk_state = scratch ? scratch + (((size_t)e * max_chunks + c) * heads + h) * HS : nullptr;
+
+    float S[NPT];
+    const float* init = pass == 0 ? slot_state : (pass == 3 ? chunk_state : nullptr);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = r * NPT + i;
+        S[i] = (init && real && n < N) ? init[(size_t)n * P + p] : 0.f;
+    }
+    float dt_sum = 0.f;
+    for (int tb = t0; tb < t1; tb += SCAN_TT) {
+        const int nt = min(SCAN_TT, t1 - tb);
+        __syncthreads();  // the previous tile is no longer read
+        for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
+            const int tt = idx / NP, n = idx % NP;
+            const T* row = xbc + (size_t)(tb + tt) * xbc_stride + inner + (size_t)g * N;
+            Bs[idx] = n < N ? to_float(row[n]) : 0.f;
+            Cs[idx] = n < N ? to_float(row[(size_t)groups * N + n]) : 0.f;
+        }
+        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+            const int tt = idx / P, q = idx % P;
+            xs[idx] = to_float(xbc[(size_t)(tb + tt) * xbc_stride + (size_t)h * P + q]);
+        }
+        if (tid < nt) {
+            const float raw = to_float(dt[(size_t)(tb + tid) * dt_stride + h]) + bias;
+            const float step = raw > 20.f ? raw : log1pf(expf(raw));  // softplus; beyond 20 the difference is below rounding
+            dts[tid] = step;
+            decs[tid] = expf(-rate * step);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float xv = real ? xs[tt * P + p] : 0.f, step = dts[tt], dec = decs[tt];
+            const float dx = step * xv;
+            const float* Bt = Bs + tt * NP + r * NPT;
+            const float* Ct = Cs + tt * NP + r * NPT;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; i += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(Bt + i), c4 = *reinterpret_cast<const float4*>(Ct + i);
+                S[i] = fmaf(dec, S[i], b4.x * dx);         acc = fmaf(S[i], c4.x, acc);
+                S[i + 1] = fmaf(dec, S[i + 1], b4.y * dx); acc = fmaf(S[i + 1], c4.y, acc);
+                S[i + 2] = fmaf(dec, S[i + 2], b4.z * dx); acc = fmaf(S[i + 2], c4.z, acc);
+                S[i + 3] = fmaf(dec, S[i + 3], b4.w * dx); acc = fmaf(S[i + 3], c4.w, acc);
+            }
+            if (pass != 1) {
+                for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (real && r == 0) y[(size_t)(tb + tt) * inner + (size_t)h * P + p] = fmaf(dskip, xv, acc);
+            }
+            dt_sum += step;
+        }
+    }
+    float* fin = pass == 1 ? chunk_state + (size_t)heads * HS /* scratch[c + 1] */ : ((pass == 0 || c == nchunks - 1) ? slot_state : nullptr);
+    if (fin && real) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = r * NPT + i;
+            if (n < N) fin[(size_t)n * P + p] = S[i];
+        }
+    }
+    if (pass == 1 && tid == 0) decay[((size_t)e * max_chunks + c) * heads + h] = expf(-rate * dt_sum);
+}
+
+// scratch[e, 0] = the slot's state; scratch[e, c] = decay[e, c - 1] * scratch[e, c - 1] + scratch[e, c] for c = 1 ..
+__global__ void __launch_bounds__(256)
+ssm_chunk_states_kernel(const float* __restrict__ state, long long slot_stride, float* __restrict__ scratch,
+                        const float* __restrict__ decay, const int* __restrict__ meta, const int* __restrict__ cu_tokens,
+                        const int* __restrict__ slots, int heads, long long HS, int chunk_len, int max_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, e = blockIdx.y;
+    if (e >= meta[META_NUM_ENTRIES]) return;
+    const int count = cu_tokens[e + 1] - cu_tokens[e], nchunks = (count + chunk_len - 1) / chunk_len;
+    const float* src = state + (size_t)slots[e] * slot_stride + (size_t)h * HS;
+    for (long long i = (long long)blockIdx.z * blockDim.x + threadIdx.x; i < HS; i += (long long)gridDim.z * blockDim.x) {
+        float s = src[i];
+        scratch[(((size_t)e * max_chunks) * heads + h) * HS + i] = s;
+        for (int c = 1; c < nchunks; ++c) {
+            float* at = scratch + (((size_t)e * max_chunks + c) * heads + h) * HS + i;
+            s = fmaf(decay[((size_t)e * max_chunks + c - 1) * heads + h], s, *at);
+            *at = s;
+        }
+    }
+}
+
+// How a head's N rows are dealt out: R threads a column, NPT rows a thread (R * NPT >= N, R a power of two).
+static bool scan_geometry(int N, int P, int* R_out, int* NPT_out) {
+    static const int sizes[] = {16, 24, 32, 48, 64};
+    int best_r = 0, best_npt = 0;
+    long best_cost = -1;
+    for (int R = 1; R <= 32; R *= 2) {
+        const int threads = ((P * R + 31) / 32) * 32;
+        if (threads > 512) break;
+        for (int k = 0; k < 5; ++k) {
+            const int npt = sizes[k];
+            if (R * npt < N) continue;
+            const long cost = (long)R * npt * 8 + (R > 1 ? R : 0);  // padded work first, then the fewest threads a column
+            if (best_cost < 0 || cost < best_cost) best_cost = cost, best_r = R, best_npt = npt;
+            break;
+        }
+    }
+    if (best_cost < 0) return false;
+    *R_out = best_r;
+    *NPT_out = best_npt;
+    return true;
+}
+
+extern "C" size_t ssm_scan_scratch_floats(int S, int heads, int P, int N, int max_chunks) {
+    return (size_t)S * max_chunks * heads * ((size_t)N * P + 1);
+}
+
+template <typename T>
+static int ssm_scan_launch(int NPT, dim3 grid, int threads, size_t smem, cudaStream_t stream, const T* xbc, int xbc_stride,
+                           const T* dt, long long dt_stride, const float* dt_bias, const float* a_log, const float* d_skip,
+                           float* state, long long slot_stride, float* y, const int* meta, const int* cu_tokens,
+                           const int* slots, int heads, int P, int N, int groups, int R, int pass, int chunk_len,
+                           int max_chunks, float* scratch, float* decay) {
+#define SCAN_CASE(K)                                                                                                       \
+    case K: {                                                                                                              \
+        static size_t configured = 0;                                                                                      \
+        if (smem > 48 * 1024 && smem > configured) {                                                                       \
+            cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (err != cudaSuccess) return (int)err;                                                                       \
+            configured = smem;                                                                                             \
+        }                                                                                                                  \
+        return (int)launch_kernel(ssm_scan_kernel<T, K>, grid, threads, smem, stream, xbc, xbc_stride, dt, dt_stride, dt_bias, \
+                                  a_log, d_skip, state, slot_stride, y, meta, cu_tokens, slots, heads, P, N, groups, R, pass,  \
+                                  chunk_len, max_chunks, scratch, decay);                                                  \
+    }
+    switch (NPT) {
+        SCAN_CASE(16) SCAN_CASE(24) SCAN_CASE(32) SCAN_CASE(48) SCAN_CASE(64)
+    }
+#undef SCAN_CASE
+    return (int)cudaErrorInvalidValue;
+}
+
+// chunk_len 0: every entry's tokens in order (one launch); else the three launches described above, with
+// `scratch` of ssm_scan_scratch_floats(S, ..., max_chunks) floats, max_chunks >= the chunks of the longest entry.
+extern "C" int ssm_scan(const void* xbc, int dtype, int xbc_stride, const void* dt, long long dt_stride, const float* dt_bias,
+                        const float* a_log, const float* d_skip, float* state, long long slot_stride, float* y,
+                        const int* meta, const int* cu_tokens, const int* slots, int S, int heads, int P, int N, int groups,
+                        int chunk_len, int max_chunks, float* scratch, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    int R = 0, NPT = 0;
+    if (heads % groups || !scan_geometry(N, P, &R, &NPT)) return (int)cudaErrorInvalidValue;
+    const int threads = ((P * R + 31) / 32) * 32;
+    const size_t smem = (size_t)(2 * SCAN_TT * R * NPT + SCAN_TT * P + 2 * SCAN_TT) * sizeof(float);
+    float* decay = scratch ? scratch + (size_t)S * max_chunks * heads * (size_t)N * P : nullptr;
+#define SCAN_PASS(TT, pass, chunks)                                                                                        \
+    ssm_scan_launch<TT>(NPT, dim3(heads, S, chunks), threads, smem, stream, (const TT*)xbc, xbc_stride, (const TT*)dt, dt_stride, \
+                        dt_bias, a_log, d_skip, state, slot_stride, y, meta, cu_tokens, slots, heads, P, N, groups, R, pass, \
+                        chunk_len, max_chunks, scratch, decay)
+    if (chunk_len <= 0 || max_chunks <= 1 || !scratch)
+        return dtype == DT_F32 ? SCAN_PASS(float, 0, 1) : SCAN_PASS(__nv_bfloat16, 0, 1);
+    int err = dtype == DT_F32 ? SCAN_PASS(float, 1, max_chunks) : SCAN_PASS(__nv_bfloat16, 1, max_chunks);
+    if (err) return err;
+    const long long HS = (long long)N * P;
+    const int zblocks = (int)((HS + 1023) / 1024);
+    err = (int)launch_kernel(ssm_chunk_states_kernel, dim3(heads, S, zblocks), 256, 0, stream, (const float*)state, slot_stride,
+                             scratch, (const float*)decay, meta, cu_tokens, slots, heads, HS, chunk_len, max_chunks);
+    if (err) return err;
+    return dtype == DT_F32 ? SCAN_PASS(float, 3, max_chunks) : SCAN_PASS(__nv_bfloat16, 3, max_chunks);
+#undef SCAN_PASS
+}
+
+// ----------------------------------------------------------------------------- gate, then the norm in equal parts
+// v = y * silu(z); out = v / sqrt(mean(v^2) + eps) * w, the mean taken over each of `parts` equal parts of the row.
+// y is float32 [T, n]; z a slice of a wider row.  One block per (token, part).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride, const float* __restrict__ w,
+                        float eps, T* __restrict__ out, const int* __restrict__ meta, int n, int parts) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, part = blockIdx.y, len = n / parts, at = part * len;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    const float* yr = y + (size_t)t * n + at;
+    const T* zr = z + (size_t)t * z_stride + at;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        const float g = to_float(zr[i]);
+        const float v = yr[i] * (g / (1.f + expf(-g)));
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)len + eps);
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        const float g = to_float(zr[i]);
+        const float v = yr[i] * (g / (1.f + expf(-g)));
+        out[(size_t)t * n + at + i] = from_float<T>(v * inv * w[at + i]);
+    }
+}
+
+extern "C" int gated_group_norm(const float* y, const void* z, int dtype, long long z_stride, const float* w, float eps,
+                                void* out, const int* meta, int T, int n, int parts, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (parts <= 0 || n % parts) return (int)cudaErrorInvalidValue;
+    const int len = n / parts, threads = len >= 1024 ? 256 : 128;
+    if (dtype == DT_F32)
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, gated_group_norm_kernel<float>, dim3(T, parts), threads, 0, stream, y,
+                                      (const float*)z, z_stride, w, eps, (float*)out, meta, n, parts);
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, gated_group_norm_kernel<__nv_bfloat16>, dim3(T, parts), threads, 0, stream,
+                                  y, (const __nv_bfloat16*)z, z_stride, w, eps, (__nv_bfloat16*)out, meta, n, parts);
+}

@@ -1,0 +1,113 @@
+// Kernels around the residual stream of blocks whose sublayers run side by side: the pending sum of several
+// terms (with a factor, rows of another stream and a vector) taken in float32 together with the norm that follows,
+// and elementwise activations.  float32 and bfloat16 storage alike; all arithmetic is float32, and every reduction
+// runs in an order that depends only on the row it belongs to.
+#include "common.cuh"
+
+int g_use_pdl = 1;
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
+
+// resid[t] <- resid[t] + mult * (a[t] + b[t]) + add_rows[t] + vec, each of a, b, add_rows, vec optional;
+// out[t] = resid[t] * rsqrt(mean(resid[t]^2) + eps) * w if `out` is given.  With `rows`: works on rows[r] of the
+// inputs, writes out[r], leaves resid untouched.  The updated row waits in shared memory between the two passes.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256)
+sum_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ a, const TD* __restrict__ b, float mult,
+                   const float* __restrict__ add_rows, const float* __restrict__ vec, const int* __restrict__ rows,
+                   const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ meta, int H) {
+    __shared__ float red[33];
+    extern __shared__ __align__(16) float row[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int limit = rows ? meta[META_NUM_ROWS] : meta[META_NUM_TOKENS];
+    if (r >= limit) return;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* x = resid + src * H;
+    const TD* pa = a ? a + src * H : nullptr;
+    const TD* pb = b ? b + src * H : nullptr;
+    const float* pr = add_rows ? add_rows + src * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[i];
+        if (pa) {
+            float s = to_float(pa[i]);
+            if (pb) s += to_float(pb[i]);
+            v = fmaf(mult, s, v);
+        }
+        if (pr) v += pr[i];
+        if (vec) v += vec[i];
+        if (!rows) x[i] = v;
+        row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!out) return;
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<TO>(row[i] * inv * w[i]);
+}
+
+extern "C" int sum_rmsnorm(float* resid, const void* a, const void* b, int term_dtype, float mult, const float* add_rows,
+                           const float* vec, const int* rows, const float* w, float eps, void* out, int out_dtype,
+                           const int* meta, int n, int H, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)H * sizeof(float);
+#define SUM_CASE(TD, TO)                                                                                                  \
+    do {                                                                                                                  \
+        static size_t configured = 0;                                                                                     \
+        if (smem > 48 * 1024 && smem > configured) {                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(sum_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                          \
+            configured = smem;                                                                                            \
+        }                                                                                                                 \
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, sum_rmsnorm_kernel<TD, TO>, n, threads, smem, stream, resid,  \
+                                      (const TD*)a, (const TD*)b, mult, add_rows, vec, rows, w, eps, (TO*)out, meta, H);  \
+    } while (0)
+    if (term_dtype == DT_F32 && out_dtype == DT_F32) SUM_CASE(float, float);
+    else if (term_dtype == DT_BF16 && out_dtype == DT_BF16) SUM_CASE(__nv_bfloat16, __nv_bfloat16);
+    else if (term_dtype == DT_F32 && out_dtype == DT_BF16) SUM_CASE(float, __nv_bfloat16);
+    else SUM_CASE(__nv_bfloat16, float);
+#undef SUM_CASE
+}
+
+// ----------------------------------------------------------------------------- elementwise activations
+// kind 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh(float z) {
+    const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+    return 0.5f * z * (1.f + tanhf(u));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+activation_kernel(const T* __restrict__ z, T* __restrict__ out, const int* __restrict__ meta, int n, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = (size_t)meta[META_NUM_TOKENS] * n;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;
+    if (i + 4 <= total && (n % 4 == 0)) {
+        float v[4];
+        load4(z + i, v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = gelu_tanh(v[k]);
+        store4(out + i, v);
+        return;
+    }
+    for (size_t k = i; k < total && k < i + 4; ++k) out[k] = from_float<T>(gelu_tanh(to_float(z[k])));
+}
+
+extern "C" int activation_rows(const void* z, void* out, int dtype, const int* meta, int T, int n, int kind,
+                               cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return 0;
+    if (kind != 0) return (int)cudaErrorInvalidValue;
+    const size_t total = (size_t)T * n;
+    const unsigned blocks = (unsigned)((total + 1023) / 1024);
+    // four elements a thread need rows that start on multiples of four elements and buffers on 16 bytes
+    if ((((uintptr_t)z | (uintptr_t)out) & 15) != 0 && n % 4 == 0) return (int)cudaErrorMisalignedAddress;
+    if (dtype == DT_F32)
+        return (int)launch_kernel(activation_kernel<float>, blocks, 256, 0, stream, (const float*)z, (float*)out, meta, n, kind);
+    return (int)launch_kernel(activation_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)z,
+                              (__nv_bfloat16*)out, meta, n, kind);
+}

@@ -29,6 +29,8 @@ ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
 GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
 DECODE_STACK_SOURCES = ["kernels/decode_stack.cu"]
+# parallel blocks, state-space mixers, latent attention, routed experts: built when a model first uses one of them
+MIXER_SOURCES = ["kernels/stream_ops.cu", "kernels/ssm.cu", "kernels/latent.cu", "kernels/moe.cu"]
 ATTENTION_TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prefill attention
 ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))  # every head size the kernels take; the build check builds them all, a model only its own
 
@@ -123,6 +125,8 @@ class CudaOps:
         self.lib.kernels_set_pdl(int(on))
         for lib in self._attn_libs.values():
             lib.kernels_set_pdl(1 if on else 0)
+        if getattr(self, "_mixer_lib", None) is not None:
+            self._mixer_lib.kernels_set_pdl(int(on))
 
     @staticmethod
     def describe_status(words) -> Optional[str]:
@@ -435,11 +439,16 @@ class CudaOps:
         its own chunk of that many positions (chunks counted from position 0 of the request).  ``sink``: the softmax
         has one more term in its denominator, a key of score 0 without a value."""
         T, S = ctx.T, ctx.S
+        # a learned sink: one float32 score per query head (a tensor) instead of the score 0 (True)
+        sinks = sink if torch.is_tensor(sink) else None
+        sink = sinks is not None or bool(sink)
+        if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nq or not sinks.is_contiguous()):
+            raise KernelError("learned sinks are one contiguous float32 score per query head")
         if (chunk or sink) and self.fast_attention(q.dtype, d, nq, nkv, q_stride) and not self.masked_fast_attention:
-            self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
-                                              _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
-                                              num_pages, window, int(chunk), int(bool(sink)), ctypes.c_float(scale),
-                                              _p(self.status), self._stream()), "attn_generic")
+            self._check(self.lib.attn_generic_sinks(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
+                                                    _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
+                                                    num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
+                                                    ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
             return
         if rope is not None and not (ctx.decode_only and self.fast_attention(q.dtype, d, nq, nkv, q_stride)):
             raise KernelError("fused rotation exists for decode steps on the bfloat16 fast path only")
@@ -471,13 +480,13 @@ class CudaOps:
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
                 if not cluster and S * nkv > self._counters.numel():
                     raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
-                self._check(lib.attn_decode_masked(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                                   _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
-                                                   rot, int(store), S, nq, nkv, page_size, num_pages,
-                                                   window, int(chunk), int(bool(sink)), ctypes.c_float(scale), splits,
-                                                   int(cluster), ctx.max_context, _p(self.status), self._stream()),
+                self._check(lib.attn_decode_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                  _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
+                                                  rot, int(store), S, nq, nkv, page_size, num_pages,
+                                                  window, int(chunk), int(bool(sink)), _p(sinks), ctypes.c_float(scale), splits,
+                                                  int(cluster), ctx.max_context, _p(self.status), self._stream()),
                             "attn_decode")
-            elif self._prefill_tc(d, page_size, nq, nkv) is not None:
+            elif sinks is None and self._prefill_tc(d, page_size, nq, nkv) is not None:  # (learned sinks: the mma.sync kernel)
                 tc = self._prefill_tc(d, page_size, nq, nkv)
                 self._check(tc.attn_prefill_tc_masked(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                                       _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
@@ -485,18 +494,183 @@ class CudaOps:
                                                       ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
                             "attn_prefill_tc")
             else:
-                self._check(lib.attn_prefill_masked(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                                    _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
-                                                    page_size, num_pages, window, int(chunk), int(bool(sink)),
-                                                    ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
+                self._check(lib.attn_prefill_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                   _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                                   page_size, num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
+                                                   ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
                             "attn_prefill")
             return
-        if d > 256:
-            raise KernelError(f"head size {d} is not supported (at most 256)")
-        self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
-                                          _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
-                                          num_pages, window, int(chunk), int(bool(sink)), ctypes.c_float(scale),
-                                          _p(self.status), self._stream()), "attn_generic")
+        if d > 512:
+            raise KernelError(f"head size {d} is not supported (at most 512)")
+        self._check(self.lib.attn_generic_sinks(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
+                                                _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
+                                                num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
+                                                ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
+
+    # ------------------------------------------------------------------ parallel blocks, state-space mixers, latent attention, experts
+    def _mixers(self):
+        lib = getattr(self, "_mixer_lib", None)
+        if lib is None:
+            lib = self._mixer_lib = build.load_library("mixers", MIXER_SOURCES, cuda=True)
+            lib.ssm_scan_scratch_floats.restype = ctypes.c_size_t
+            lib.kernels_set_pdl(int(self.pdl))
+        return lib
+
+    @staticmethod
+    def _rows(t, what: str):
+        """(pointer, elements from row to row) of a 2-d slice whose rows are contiguous."""
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"{what}: rows must be contiguous, got strides {t.stride()}")
+        return _p(t), ctypes.c_longlong(t.stride(0))
+
+    @staticmethod
+    def _heads(t, what: str):
+        """(pointer, token stride, head stride) of a [T, heads, n] slice whose last axis is contiguous."""
+        if t.dim() != 3 or t.stride(2) != 1:
+            raise KernelError(f"{what}: the last axis must be contiguous, got strides {t.stride()}")
+        return _p(t), ctypes.c_longlong(t.stride(0)), ctypes.c_longlong(t.stride(1))
+
+    def sum_rmsnorm(self, resid, pending, w, eps: float, out, meta, n: int, rows=None):
+        """resid += mult * (sum of pending.terms) + pending.rows + pending.vector, each optional, in float32;
+        out = rmsnorm(resid) * w if ``out`` is given.  With ``rows`` the sum and the norm are taken at those rows only and
+        resid is left as it is."""
+        terms = list(pending.terms) if pending is not None else []
+        if len(terms) > 2 or len({t.dtype for t in terms}) > 1:
+            raise KernelError("a pending sum has at most two terms, of one type")
+        a, b = (terms + [None, None])[:2]
+        tcode = _code(a) if a is not None else DT_F32
+        self._check(self._mixers().sum_rmsnorm(_p(resid), _p(a), _p(b), tcode, ctypes.c_float(pending.mult if pending else 1.0),
+                                               _p(pending.rows if pending else None), _p(pending.vector if pending else None),
+                                               _p(rows), _p(w), ctypes.c_float(eps), _p(out),
+                                               _code(out) if out is not None else DT_F32, _p(meta), n, resid.shape[-1],
+                                               self._stream()), "sum_rmsnorm")
+
+    def activation(self, z, out, kind: str, meta):
+        """out = act(z) element by element; ``kind``: "gelu_tanh"."""
+        code = {"gelu_tanh": 0}[kind]
+        self._check(self._mixers().activation_rows(_p(z), _p(out), _code(z), _p(meta), z.shape[0], z.shape[1], code,
+                                                   self._stream()), "activation_rows")
+
+    def causal_conv_act(self, u, w, bias, state, ctx, out, *, act: str = "silu"):
+        """out[t] = act(bias + sum_j w[j] * u[t - taps + 1 + j]) over the rows of each request, zeros before its start; ``u``
+        a slice of wider rows, ``w`` float32 [taps, C], ``bias`` float32 [C] or None; rows before the step's portion come
+        from ``state`` (float32 [slots, taps - 1, C], the row of position p at place p mod (taps - 1)), which
+        ``causal_conv_save`` writes afterwards."""
+        taps, C = w.shape
+        up, us = self._rows(u, "causal_conv_act")
+        self._check(self._mixers().causal_conv_act(up, _code(u), us, _p(w), _p(bias), _p(state), self._slot_stride(state), _p(out),
+                                                   _p(ctx.meta), _p(ctx.positions), _p(ctx.token_entry), _p(ctx.cu_tokens),
+                                                   _p(ctx.state_slots), ctx.T, C, taps, {"none": 0, "silu": 1}[act],
+                                                   self._stream()), "causal_conv_act")
+
+    def causal_conv_save(self, u, state, ctx, taps: int):
+        """The last taps - 1 rows of u of every entry go to its state (see ``causal_conv_act``)."""
+        if taps > 1:
+            up, us = self._rows(u, "causal_conv_save")
+            self._check(self._mixers().causal_conv_save(up, _code(u), us, _p(state), self._slot_stride(state), _p(ctx.meta),
+                                                        _p(ctx.positions), _p(ctx.token_entry), _p(ctx.cu_tokens),
+                                                        _p(ctx.state_slots), ctx.T, u.shape[1], taps, self._stream()),
+                        "causal_conv_save")
+
+    SCAN_CHUNK = 64        # tokens of a chunk when a long portion's recurrence is cut into chunks that run side by side
+    SCAN_CHUNK_FROM = 128  # ... which happens from this many tokens of the step's longest entry on
+
+    def ssm_scan(self, xbc, dt, dt_bias, a_log, d_skip, state, ctx, y, *, heads: int, head_dim: int, nstate: int, groups: int):
+        """The state-space recurrence of every entry's tokens: rows of ``xbc`` are [x | B | C], ``dt`` a slice of wider
+        rows (softplus(dt + dt_bias) is taken here), ``state`` float32 [slots, heads, nstate, head_dim] (read and
+        updated), ``y`` float32 [T, heads * head_dim]."""
+        if state.dim() != 4 or state[0].is_contiguous() is False or state.dtype != torch.float32:
+            raise KernelError("a recurrence state is float32 [slots, heads, rows, columns] with contiguous slots")
+        dp, ds = self._rows(dt, "ssm_scan")
+        lib = self._mixers()
+        longest = ctx.max_tokens_per_entry
+        chunk = self.SCAN_CHUNK if longest >= self.SCAN_CHUNK_FROM else 0
+        while chunk and longest // chunk > 256:
+            chunk *= 2
+        chunks = -(-longest // chunk) if chunk else 1
+        scratch = (torch.empty(lib.ssm_scan_scratch_floats(ctx.S, heads, head_dim, nstate, chunks), dtype=torch.float32,
+                               device=y.device) if chunk else None)
+        self._check(lib.ssm_scan(_p(xbc), _code(xbc), xbc.stride(0), dp, ds, _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
+                                 ctypes.c_longlong(state.stride(0)), _p(y), _p(ctx.meta), _p(ctx.cu_tokens), _p(ctx.state_slots),
+                                 ctx.S, heads, head_dim, nstate, groups, chunk, chunks, _p(scratch), self._stream()), "ssm_scan")
+        if chunk:
+            self.launches += 2
+
+    def gated_group_norm(self, y, z, w, groups: int, eps: float, out, meta):
+        """out = v / sqrt(mean(v^2) + eps) * w with v = y * silu(z), the mean over each of ``groups`` equal parts of a row;
+        ``y`` float32 [T, n], ``z`` a slice of wider rows."""
+        zp, zs = self._rows(z, "gated_group_norm")
+        self._check(self._mixers().gated_group_norm(_p(y), zp, _code(z), zs, _p(w), ctypes.c_float(eps), _p(out), _p(meta),
+                                                    y.shape[0], y.shape[1], groups, self._stream()), "gated_group_norm")
+
+    def rms_rows(self, x, w, eps: float, out, meta):
+        """out = x * rsqrt(mean(x^2) + eps) * w row by row; ``x`` a slice of wider rows, ``w`` float32."""
+        xp, xs = self._rows(x, "rms_rows")
+        self._check(self._mixers().rms_rows(xp, _code(x), xs, _p(w), ctypes.c_float(eps), _p(out), _p(meta), x.shape[0], x.shape[1],
+                                            self._stream()), "rms_rows")
+
+    HEAD_LINEAR_LIBRARY_ROWS = 64  # from this many rows on, a bfloat16 map per head is a batched library product
+
+    def head_linear(self, x, w, out, meta, gate=None):
+        """out[t, h] = w[h] x[t, h] (times sigmoid(gate[t, h]) if given): x [T, heads, K], out and gate [T, heads, N] slices
+        with a contiguous last axis, w [heads, N, K] contiguous."""
+        heads, N, K = w.shape
+        T = x.shape[0]
+        lib = self._mixers()
+        op, ot, oh = self._heads(out, "head_linear")
+        gp, gt, gh = self._heads(gate, "head_linear") if gate is not None else (None, ctypes.c_longlong(0), ctypes.c_longlong(0))
+        if x.dtype == torch.bfloat16 and T >= self.HEAD_LINEAR_LIBRARY_ROWS:
+            out.copy_(torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1))
+            if gate is not None:
+                self._check(lib.sigmoid_gate(op, ot, oh, gp, gt, gh, _code(out), _p(meta), T, heads, N, self._stream()),
+                            "sigmoid_gate")
+            return
+        xp, xt, xh = self._heads(x, "head_linear")
+        self._check(lib.head_linear(xp, xt, xh, _p(w), op, ot, oh, gp, gt, gh, _code(x), _p(meta), T, heads, K, N,
+                                    self._stream()), "head_linear")
+
+    def latent_rows(self, q_rot, q_abs, dkv, norm_w, eps: float, ctx, cache_layer, group: int, q_out, *, heads: int,
+                    kv_rank: int, rot_dim: int, padded: int, page_size: int, num_pages: int, store: bool, inv_freq=None,
+                    rotary_dims: int = 0):
+        """The rows of latent attention.  The cached vector [rmsnorm(dkv[:kv_rank]) * norm_w | rotated dkv[kv_rank:] |
+        zeros] of ``padded`` elements goes to the key plane and the value plane of the token's page; the queries become
+        [q_abs[h] | rotated q_rot[h] | zeros] in ``q_out`` [T, heads * padded].  Rotation: of the first ``rotary_dims``
+        dimensions, 2i pairs with 2i + 1, angle position * inv_freq[i]."""
+        qp, qt, qh = self._heads(q_rot, "latent_rows")
+        dp, ds = self._rows(dkv, "latent_rows")
+        if not q_abs.is_contiguous():
+            raise KernelError("latent_rows: q_abs must be contiguous")
+        self._check(self._mixers().latent_rows(qp, qt, qh, _p(q_abs), dp, ds, _p(norm_w), ctypes.c_float(eps), _p(ctx.positions),
+                                               _p(ctx.token_entry), _p(ctx.meta), max(group, 0), _p(inv_freq),
+                                               int(rotary_dims) if inv_freq is not None else 0, _p(q_out), _p(cache_layer),
+                                               _code(q_out), ctx.T, heads, kv_rank, rot_dim, padded, page_size, num_pages,
+                                               int(store), _p(self.status), self._stream()), "latent_rows")
+
+    def moe_route(self, h, w_router, ids, wts, meta):
+        """Per token: float32 logits w_router h, softmax over all experts, the ids.shape[1] largest scores (ties to the
+        lower index) into ``ids`` (int32) and those scores divided by their sum (+ 1e-20) into ``wts`` (float32)."""
+        E, H = w_router.shape
+        self._check(self._mixers().moe_route(_p(h), _code(h), _p(w_router), _p(ids), _p(wts), _p(meta), h.shape[0], H, E,
+                                             ids.shape[1], self._stream()), "moe_route")
+
+    def moe_experts(self, h, ids, wts, w_gate_up, w_down, shared, out, meta):
+        """out[t] = sum_k wts[t, k] * expert ids[t, k] of h[t] (+ shared[t]); an expert is down(silu(gate x) * up x) with
+        ``w_gate_up`` [E, 2F, H] (gate rows first) and ``w_down`` [E, H, F].  The (token, choice) pairs are sorted by expert
+        on the device and the two linears run as grouped products over that order."""
+        T, top = ids.shape
+        E, F2, H = w_gate_up.shape
+        F = F2 // 2
+        lib, dev = self._mixers(), h.device
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        order = torch.empty(T * top, dtype=torch.int32, device=dev)
+        self._check(lib.moe_sort(_p(ids), _p(offsets), _p(order), _p(meta), top, E, self._stream()), "moe_sort")
+        act = torch.empty((T * top, F), dtype=h.dtype, device=dev)
+        y = torch.empty((T * top, H), dtype=torch.float32, device=dev)
+        self._check(lib.moe_grouped_ff(_p(h), _p(w_gate_up), _p(act), _p(w_down), _p(y), _p(offsets), _p(order), _code(h), T, top,
+                                       E, H, F, self._stream()), "moe_grouped_ff")
+        self.launches += 1
+        self._check(lib.moe_combine(_p(y), _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top, H, self._stream()),
+                    "moe_combine")
 
     # ------------------------------------------------------------------ whole layers of a decode step
     def _decode_stack_library(self, d: int):
