@@ -38,45 +38,55 @@ extern "C" int rms_rows(const void* x, int dtype, long long x_stride, const floa
 
 // ----------------------------------------------------------------------------- a linear map per head
 // y[t, h, n] = sum_k x[t, h, k] * w[h, n, k] (optionally times sigmoid(gate[t, h, n])).  x, y and gate are slices:
-// element (t, h, i) lies at t * stride_t + h * stride_h + i.  A block takes HL_TM tokens x HL_TN outputs of one head;
-// x and w tiles go through shared memory HL_KC columns at a time; every output is one accumulator running over k in
-// order, so its value does not depend on the tile it falls in.
+// element (t, h, i) lies at t * stride_t + h * stride_h + i.
 #define HL_TM 8
 #define HL_TN 128
-#define HL_KC 32
+#define HL_KC 512
+// A block takes HL_TM tokens x HL_TN outputs of one head.  The tokens' x waits in shared memory (HL_KC columns at a
+// time); a thread owns one output and reads its weight row itself, 16 bytes a load where the rows allow; every output
+// is one accumulator running over k in order, so its value does not depend on the tile it falls in.
 template <typename T>
 __global__ void __launch_bounds__(HL_TN)
 head_linear_kernel(const T* __restrict__ x, long long xs_t, long long xs_h, const T* __restrict__ w, T* __restrict__ y,
                    long long ys_t, long long ys_h, const T* __restrict__ gate, long long gs_t, long long gs_h,
-                   const int* __restrict__ meta, int K, int N) {
+                   const int* __restrict__ meta, int K, int N, int wvec) {
     __shared__ float xs[HL_TM][HL_KC];
-    __shared__ float ws[HL_TN][HL_KC + 1];
     pdl_launch_dependents();
     pdl_wait();
     const int ntok = meta[META_NUM_TOKENS];
-    const int t0 = blockIdx.x * HL_TM, h = blockIdx.y, n0 = blockIdx.z * HL_TN, tid = threadIdx.x;
+    const int t0 = blockIdx.x * HL_TM, h = blockIdx.y, n0 = blockIdx.z * blockDim.x, tid = threadIdx.x;
     if (t0 >= ntok) return;
     const int rows = min(HL_TM, ntok - t0), n = n0 + tid;
-    const T* wh = w + (size_t)h * N * K;
+    const T* wr = w + ((size_t)h * N + min(n, N - 1)) * K;
+    constexpr int V = 16 / sizeof(T);
     float acc[HL_TM];
 #pragma unroll
     for (int m = 0; m < HL_TM; ++m) acc[m] = 0.f;
     for (int k0 = 0; k0 < K; k0 += HL_KC) {
         const int kc = min(HL_KC, K - k0);
         __syncthreads();
-        for (int idx = tid; idx < HL_TM * HL_KC; idx += HL_TN) {
-            const int m = idx / HL_KC, kk = idx % HL_KC;
-            xs[m][kk] = (m < rows && kk < kc) ? to_float(x[(size_t)(t0 + m) * xs_t + (size_t)h * xs_h + k0 + kk]) : 0.f;
-        }
-        for (int idx = tid; idx < HL_TN * HL_KC; idx += HL_TN) {
-            const int j = idx / HL_KC, kk = idx % HL_KC;
-            ws[j][kk] = (n0 + j < N && kk < kc) ? to_float(wh[(size_t)(n0 + j) * K + k0 + kk]) : 0.f;
+        for (int idx = tid; idx < HL_TM * kc; idx += blockDim.x) {
+            const int m = idx / kc, kk = idx % kc;
+            xs[m][kk] = m < rows ? to_float(x[(size_t)(t0 + m) * xs_t + (size_t)h * xs_h + k0 + kk]) : 0.f;
         }
         __syncthreads();
-        for (int kk = 0; kk < kc; ++kk) {
-            const float wv = ws[tid][kk];
+        int kk = 0;
+        if (wvec) {
+            for (; kk + V <= kc; kk += V) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(wr + k0 + kk);
+                const T* wv = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-            for (int m = 0; m < HL_TM; ++m) acc[m] = fmaf(xs[m][kk], wv, acc[m]);
+                for (int i = 0; i < V; ++i) {
+                    const float f = to_float(wv[i]);
+#pragma unroll
+                    for (int m = 0; m < HL_TM; ++m) acc[m] = fmaf(xs[m][kk + i], f, acc[m]);
+                }
+            }
+        }
+        for (; kk < kc; ++kk) {
+            const float f = to_float(wr[k0 + kk]);
+#pragma unroll
+            for (int m = 0; m < HL_TM; ++m) acc[m] = fmaf(xs[m][kk], f, acc[m]);
         }
     }
     if (n >= N) return;
@@ -94,13 +104,16 @@ extern "C" int head_linear(const void* x, long long xs_t, long long xs_h, const 
                            long long ys_h, const void* gate, long long gs_t, long long gs_h, int dtype, const int* meta, int T,
                            int heads, int K, int N, cudaStream_t stream) {
     if (T <= 0) return 0;
-    dim3 grid((T + HL_TM - 1) / HL_TM, heads, (N + HL_TN - 1) / HL_TN);
+    const int tn = N <= 32 ? 32 : (N <= 64 ? 64 : HL_TN);  // few outputs a head: smaller blocks, all of their threads at work
+    dim3 grid((T + HL_TM - 1) / HL_TM, heads, (N + tn - 1) / tn);
+    const int elem = dtype == DT_F32 ? 4 : 2;
+    const int wvec = ((size_t)K * elem) % 16 == 0 && ((uintptr_t)w & 15) == 0;
     if (dtype == DT_F32)
-        return (int)launch_kernel(head_linear_kernel<float>, grid, HL_TN, 0, stream, (const float*)x, xs_t, xs_h, (const float*)w,
-                                  (float*)y, ys_t, ys_h, (const float*)gate, gs_t, gs_h, meta, K, N);
-    return (int)launch_kernel(head_linear_kernel<__nv_bfloat16>, grid, HL_TN, 0, stream, (const __nv_bfloat16*)x, xs_t, xs_h,
+        return (int)launch_kernel(head_linear_kernel<float>, grid, tn, 0, stream, (const float*)x, xs_t, xs_h, (const float*)w,
+                                  (float*)y, ys_t, ys_h, (const float*)gate, gs_t, gs_h, meta, K, N, wvec);
+    return (int)launch_kernel(head_linear_kernel<__nv_bfloat16>, grid, tn, 0, stream, (const __nv_bfloat16*)x, xs_t, xs_h,
                               (const __nv_bfloat16*)w, (__nv_bfloat16*)y, ys_t, ys_h, (const __nv_bfloat16*)gate, gs_t, gs_h,
-                              meta, K, N);
+                              meta, K, N, wvec);
 }
 
 // y[t, h, n] *= sigmoid(gate[t, h, n]) for a product that a library made (same slices as above).
@@ -135,8 +148,9 @@ extern "C" int sigmoid_gate(void* y, long long ys_t, long long ys_h, const void*
 // goes to the key plane and to the value plane of the token's page (one key/value head of D elements); the queries
 // become [q_abs[h] | rotated q_rot[h] | zeros] of D elements a head.  Rotation: of the first `rot` dimensions of a
 // rotated part, 2i pairs with 2i + 1, by the angle position * inv_freq[i] (float32 product, sincosf).
+// One block per (token, query head), and one more per token (block y = heads) for the cached vector.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 latent_rows_kernel(const T* __restrict__ q_rot, long long qs_t, long long qs_h, const T* __restrict__ q_abs,
                    const T* __restrict__ dkv, long long dkv_stride, const float* __restrict__ norm_w, float eps,
                    const int* __restrict__ positions, const int* __restrict__ token_entry, const int* __restrict__ meta,
@@ -146,67 +160,71 @@ latent_rows_kernel(const T* __restrict__ q_rot, long long qs_t, long long qs_h, 
     extern __shared__ float cs[];  // rot / 2 cosines, rot / 2 sines
     float* sn = cs + rot / 2;
     // The step's metadata is written by no kernel of the step: it is read before the wait.
-    const int t = blockIdx.x, tid = threadIdx.x;
-    const bool live = t < meta[META_NUM_TOKENS];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const bool live = t < meta[META_NUM_TOKENS] && (h < heads || store);
     const int p = live ? positions[t] : 0;
     int page = 0;
-    if (live && store) page = (meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group])[p / page_size];
-    for (int i = tid; i < rot / 2; i += blockDim.x) sincosf((float)p * inv_freq[i], &sn[i], &cs[i]);
+    if (live && h == heads) page = (meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group])[p / page_size];
+    if (live)
+        for (int i = tid; i < rot / 2; i += blockDim.x) sincosf((float)p * inv_freq[i], &sn[i], &cs[i]);
     pdl_wait();
     pdl_launch_dependents();
     if (!live) return;
+    __syncthreads();  // the cosines and sines are written
+    if (h < heads) {
+        const T* qr = q_rot + (size_t)t * qs_t + (size_t)h * qs_h;
+        const T* qa = q_abs + ((size_t)t * heads + h) * rank;
+        T* dst = q_out + ((size_t)t * heads + h) * D;
+        for (int i = tid; i < D; i += blockDim.x) {
+            float v = 0.f;
+            if (i < rank) {
+                v = to_float(qa[i]);
+            } else if (i < rank + rdim) {
+                const int j = i - rank;
+                v = to_float(qr[j]);
+                if (j < rot) {
+                    const float other = to_float(qr[j ^ 1]);
+                    float lo, hi;
+                    if (j & 1) { rotate_pair(other, v, cs[j >> 1], sn[j >> 1], lo, hi); v = hi; }
+                    else { rotate_pair(v, other, cs[j >> 1], sn[j >> 1], lo, hi); v = lo; }
+                }
+            }
+            dst[i] = from_float<T>(v);
+        }
+        return;
+    }
     const T* kv = dkv + (size_t)t * dkv_stride;
     float ss = 0.f;
     for (int i = tid; i < rank; i += blockDim.x) {
         const float v = to_float(kv[i]);
         ss = fmaf(v, v, ss);
     }
-    ss = block_sum(ss, red);  // (its barriers also publish the cosines and sines)
+    ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)rank + eps);
-    if (store) {
-        if (page <= 0 || page >= num_pages) {
-            if (tid == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
-        } else {
-            CacheLayout L{1, page_size, D};
-            T* kdst = cache + L.offset(page, 0, 0, p % page_size);
-            T* vdst = cache + L.offset(page, 1, 0, p % page_size);
-            for (int i = tid; i < D; i += blockDim.x) {
-                float v = 0.f;
-                if (i < rank) {
-                    v = to_float(kv[i]) * inv * norm_w[i];
-                } else if (i < rank + rdim) {
-                    const int j = i - rank;
-                    v = to_float(kv[i]);
-                    if (j < rot) {
-                        const float other = to_float(kv[rank + (j ^ 1)]);
-                        float lo, hi;
-                        if (j & 1) { rotate_pair(other, v, cs[j >> 1], sn[j >> 1], lo, hi); v = hi; }
-                        else { rotate_pair(v, other, cs[j >> 1], sn[j >> 1], lo, hi); v = lo; }
-                    }
-                }
-                const T o = from_float<T>(v);
-                kdst[i] = o;
-                vdst[i] = o;
-            }
-        }
+    if (page <= 0 || page >= num_pages) {
+        if (tid == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+        return;
     }
-    for (int idx = tid; idx < heads * D; idx += blockDim.x) {
-        const int h = idx / D, i = idx % D;
+    CacheLayout L{1, page_size, D};
+    T* kdst = cache + L.offset(page, 0, 0, p % page_size);
+    T* vdst = cache + L.offset(page, 1, 0, p % page_size);
+    for (int i = tid; i < D; i += blockDim.x) {
         float v = 0.f;
         if (i < rank) {
-            v = to_float(q_abs[((size_t)t * heads + h) * rank + i]);
+            v = to_float(kv[i]) * inv * norm_w[i];
         } else if (i < rank + rdim) {
             const int j = i - rank;
-            const T* qr = q_rot + (size_t)t * qs_t + (size_t)h * qs_h;
-            v = to_float(qr[j]);
+            v = to_float(kv[i]);
             if (j < rot) {
-                const float other = to_float(qr[j ^ 1]);
+                const float other = to_float(kv[rank + (j ^ 1)]);
                 float lo, hi;
                 if (j & 1) { rotate_pair(other, v, cs[j >> 1], sn[j >> 1], lo, hi); v = hi; }
                 else { rotate_pair(v, other, cs[j >> 1], sn[j >> 1], lo, hi); v = lo; }
             }
         }
-        q_out[(size_t)t * heads * D + idx] = from_float<T>(v);
+        const T o = from_float<T>(v);
+        kdst[i] = o;
+        vdst[i] = o;
     }
 }
 
@@ -219,11 +237,11 @@ extern "C" int latent_rows(const void* q_rot, long long qs_t, long long qs_h, co
     if (rot % 2 || rot > rdim || rank + rdim > D || (rot && !inv_freq)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)rot * sizeof(float);
     if (dtype == DT_F32)
-        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<float>, T, 256, smem, stream, (const float*)q_rot, qs_t,
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<float>, dim3(T, heads + 1), 128, smem, stream, (const float*)q_rot, qs_t,
                                       qs_h, (const float*)q_abs, (const float*)dkv, dkv_stride, norm_w, eps, positions, token_entry,
                                       meta, group, inv_freq, rot, (float*)q_out, (float*)cache, heads, rank, rdim, D, page_size,
                                       num_pages, store, status);
-    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<__nv_bfloat16>, T, 256, smem, stream,
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<__nv_bfloat16>, dim3(T, heads + 1), 128, smem, stream,
                                   (const __nv_bfloat16*)q_rot, qs_t, qs_h, (const __nv_bfloat16*)q_abs, (const __nv_bfloat16*)dkv,
                                   dkv_stride, norm_w, eps, positions, token_entry, meta, group, inv_freq, rot,
                                   (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, heads, rank, rdim, D, page_size, num_pages, store,

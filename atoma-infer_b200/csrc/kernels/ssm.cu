@@ -38,12 +38,92 @@ causal_conv_act_kernel(const T* __restrict__ u, long long u_stride, const float*
     }
 }
 
+// The same, V channels a thread with 16-byte accesses (V = 4 for float32, 8 for bfloat16; C, u_stride and slot_stride
+// multiples of V, buffers on 16 bytes), the channels of a row dealt out over blocks (grid y).  save_own: every entry of
+// the step brings one token, so the thread that read a channel's ring also writes the new row's place (p mod R, whose old
+// row, of position p - R, it has just read): the ring is updated here and causal_conv_save is not needed.
+template <typename T, int V>
+__global__ void __launch_bounds__(128)
+causal_conv_act_vec_kernel(const T* __restrict__ u, long long u_stride, const float* __restrict__ w,
+                           const float* __restrict__ bias, float* __restrict__ state, long long slot_stride,
+                           T* __restrict__ y, const int* __restrict__ meta, const int* __restrict__ positions,
+                           const int* __restrict__ token_entry, const int* __restrict__ cu_tokens,
+                           const int* __restrict__ slots, int C, int taps, int act, int save_own) {
+    const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    const bool live = t < meta[META_NUM_TOKENS] && c < C;
+    const int e = live ? token_entry[t] : 0, p = live ? positions[t] : 0, first = live ? cu_tokens[e] : 0, R = taps - 1;
+    float* st = state ? state + (size_t)(live ? slots[e] : 0) * slot_stride : nullptr;
+    float acc[V];
+    if (live) {  // weights and bias depend on no earlier kernel: fetched before the wait
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+            float b4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (bias) load4(bias + c + i, b4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[i + k] = b4[k];
+        }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!live) return;
+    float cur[V];
+    for (int j = 0; j < taps; ++j) {  // oldest tap first: a fixed order
+        const int back = taps - 1 - j, src = p - back;
+        if (src < 0) continue;
+        float v[V], wv[V];
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+            float t4[4], w4[4];
+            if (t - back >= first) load4(u + (size_t)(t - back) * u_stride + c + i, t4);
+            else load4(st + (size_t)(src % R) * C + c + i, t4);
+            load4(w + (size_t)j * C + c + i, w4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[i + k] = t4[k], wv[i + k] = w4[k];
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(wv[i], v[i], acc[i]);
+        if (back == 0) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) cur[i] = v[i];
+        }
+    }
+    if (act == 1) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = acc[i] / (1.f + expf(-acc[i]));
+    }
+#pragma unroll
+    for (int i = 0; i < V; i += 4) {
+        const float o4[4] = {acc[i], acc[i + 1], acc[i + 2], acc[i + 3]};
+        store4(y + (size_t)t * C + c + i, o4);
+    }
+    if (save_own && R > 0) {
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+            const float s4[4] = {cur[i], cur[i + 1], cur[i + 2], cur[i + 3]};
+            store4(st + (size_t)(p % R) * C + c + i, s4);
+        }
+    }
+}
+
 extern "C" int causal_conv_act(const void* u, int dtype, long long u_stride, const float* w, const float* bias,
-                               const float* state, long long slot_stride, void* y, const int* meta, const int* positions,
+                               float* state, long long slot_stride, void* y, const int* meta, const int* positions,
                                const int* token_entry, const int* cu_tokens, const int* slots, int T, int C, int taps,
-                               int act, cudaStream_t stream) {
+                               int act, int save_own, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (taps < 1 || (taps > 1 && !state)) return (int)cudaErrorInvalidValue;
+    const int V = dtype == DT_F32 ? 4 : 8;
+    if (C % V == 0 && u_stride % V == 0 && slot_stride % 4 == 0 &&
+        (((uintptr_t)u | (uintptr_t)w | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)y) & 15) == 0) {
+        dim3 grid(T, (C / V + 127) / 128);
+        if (dtype == DT_F32)
+            return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, causal_conv_act_vec_kernel<float, 4>, grid, 128, 0, stream,
+                                          (const float*)u, u_stride, w, bias, (float*)state, slot_stride, (float*)y, meta, positions,
+                                          token_entry, cu_tokens, slots, C, taps, act, save_own);
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, causal_conv_act_vec_kernel<__nv_bfloat16, 8>, grid, 128, 0, stream,
+                                      (const __nv_bfloat16*)u, u_stride, w, bias, (float*)state, slot_stride, (__nv_bfloat16*)y, meta,
+                                      positions, token_entry, cu_tokens, slots, C, taps, act, save_own);
+    }
+    if (save_own) return (int)cudaErrorInvalidValue;  // (ask causal_conv_act_saves first)
     const int threads = C >= 1024 ? 256 : 128;
     if (dtype == DT_F32)
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, causal_conv_act_kernel<float>, T, threads, 0, stream, (const float*)u,
@@ -52,6 +132,14 @@ extern "C" int causal_conv_act(const void* u, int dtype, long long u_stride, con
     return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, causal_conv_act_kernel<__nv_bfloat16>, T, threads, 0, stream,
                                   (const __nv_bfloat16*)u, u_stride, w, bias, state, slot_stride, (__nv_bfloat16*)y, meta,
                                   positions, token_entry, cu_tokens, slots, C, taps, act);
+}
+
+// Whether causal_conv_act can update the ring itself (see save_own) for these sizes and addresses.
+extern "C" int causal_conv_act_saves(const void* u, int dtype, long long u_stride, const float* w, const float* bias,
+                                     const float* state, long long slot_stride, const void* y, int C) {
+    const int V = dtype == DT_F32 ? 4 : 8;
+    return C % V == 0 && u_stride % V == 0 && slot_stride % 4 == 0 &&
+           (((uintptr_t)u | (uintptr_t)w | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)y) & 15) == 0;
 }
 
 // The last R rows of u of every entry go to its ring.
@@ -99,13 +187,29 @@ extern "C" int causal_conv_save(const void* u, int dtype, long long u_stride, fl
 // pass 3: chunk c runs again from scratch[c] and writes y; the last chunk updates the slot.
 #define SCAN_TT 16
 
-template <typename T, int NPT>
+// Eight (bfloat16) or four (float32) consecutive elements of a row, widened, into shared memory.
+__device__ __forceinline__ void stage8(const __nv_bfloat16* src, float* dst) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        dst[2 * i] = f.x;
+        dst[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void stage8(const float* src, float* dst) {
+    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+}
+
+template <typename T, int NPT, bool WRITE_Y>
 __global__ void __launch_bounds__(512)
 ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__ dt, long long dt_stride,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, float* __restrict__ y, const int* __restrict__ meta,
                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads, int P, int N, int groups, int R,
-                int pass, int chunk_len, int max_chunks, float* __restrict__ scratch, float* __restrict__ decay) {
+                int pass, int chunk_len, int max_chunks, float* __restrict__ scratch, float* __restrict__ decay, int vec8) {
     extern __shared__ __align__(16) float sm[];
     const int NP = R * NPT;                 // padded N
     float* Bs = sm;                         // [SCAN_TT][NP]
@@ -140,15 +244,33 @@ ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__
     for (int tb = t0; tb < t1; tb += SCAN_TT) {
         const int nt = min(SCAN_TT, t1 - tb);
         __syncthreads();  // the previous tile is no longer read
-        for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
-            const int tt = idx / NP, n = idx % NP;
-            const T* row = xbc + (size_t)(tb + tt) * xbc_stride + inner + (size_t)g * N;
-            Bs[idx] = n < N ? to_float(row[n]) : 0.f;
-            Cs[idx] = n < N ? to_float(row[(size_t)groups * N + n]) : 0.f;
-        }
-        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
-            const int tt = idx / P, q = idx % P;
-            xs[idx] = to_float(xbc[(size_t)(tb + tt) * xbc_stride + (size_t)h * P + q]);
+        if (vec8) {  // a warp a row, a lane eight elements a step: every load of the tile is in flight at once
+            const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+            for (int tt = warp; tt < nt; tt += nwarps) {
+                const T* row = xbc + (size_t)(tb + tt) * xbc_stride;
+                const T* brow = row + inner + (size_t)g * N;
+                for (int n = lane * 8; n < NP; n += 256) {
+                    if (n < N) {
+                        stage8(brow + n, Bs + tt * NP + n);
+                        stage8(brow + (size_t)groups * N + n, Cs + tt * NP + n);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) Bs[tt * NP + n + i] = Cs[tt * NP + n + i] = 0.f;
+                    }
+                }
+                for (int q = lane * 8; q < P; q += 256) stage8(row + (size_t)h * P + q, xs + tt * P + q);
+            }
+        } else {
+            for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
+                const int tt = idx / NP, n = idx % NP;
+                const T* row = xbc + (size_t)(tb + tt) * xbc_stride + inner + (size_t)g * N;
+                Bs[idx] = n < N ? to_float(row[n]) : 0.f;
+                Cs[idx] = n < N ? to_float(row[(size_t)groups * N + n]) : 0.f;
+            }
+            for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+                const int tt = idx / P, q = idx % P;
+                xs[idx] = to_float(xbc[(size_t)(tb + tt) * xbc_stride + (size_t)h * P + q]);
+            }
         }
         if (tid < nt) {
             const float raw = to_float(dt[(size_t)(tb + tid) * dt_stride + h]) + bias;
@@ -165,13 +287,20 @@ ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < NPT; i += 4) {
-                const float4 b4 = *reinterpret_cast<const float4*>(Bt + i), c4 = *reinterpret_cast<const float4*>(Ct + i);
-                S[i] = fmaf(dec, S[i], b4.x * dx);         acc = fmaf(S[i], c4.x, acc);
-                S[i + 1] = fmaf(dec, S[i + 1], b4.y * dx); acc = fmaf(S[i + 1], c4.y, acc);
-                S[i + 2] = fmaf(dec, S[i + 2], b4.z * dx); acc = fmaf(S[i + 2], c4.z, acc);
-                S[i + 3] = fmaf(dec, S[i + 3], b4.w * dx); acc = fmaf(S[i + 3], c4.w, acc);
+                const float4 b4 = *reinterpret_cast<const float4*>(Bt + i);
+                S[i] = fmaf(dec, S[i], b4.x * dx);
+                S[i + 1] = fmaf(dec, S[i + 1], b4.y * dx);
+                S[i + 2] = fmaf(dec, S[i + 2], b4.z * dx);
+                S[i + 3] = fmaf(dec, S[i + 3], b4.w * dx);
+                if (WRITE_Y) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(Ct + i);
+                    acc = fmaf(S[i], c4.x, acc);
+                    acc = fmaf(S[i + 1], c4.y, acc);
+                    acc = fmaf(S[i + 2], c4.z, acc);
+                    acc = fmaf(S[i + 3], c4.w, acc);
+                }
             }
-            if (pass != 1) {
+            if (WRITE_Y) {
                 for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                 if (real && r == 0) y[(size_t)(tb + tt) * inner + (size_t)h * P + p] = fmaf(dskip, xv, acc);
             }
@@ -243,20 +372,24 @@ static int ssm_scan_launch(int NPT, dim3 grid, int threads, size_t smem, cudaStr
                            float* state, long long slot_stride, float* y, const int* meta, const int* cu_tokens,
                            const int* slots, int heads, int P, int N, int groups, int R, int pass, int chunk_len,
                            int max_chunks, float* scratch, float* decay) {
-#define SCAN_CASE(K)                                                                                                       \
+    // eight elements a load: rows of x, B and C that start on 16 bytes (float32: two loads of four)
+    const int vec8 = P % 8 == 0 && N % 8 == 0 && xbc_stride % 8 == 0 && ((uintptr_t)xbc & 15) == 0 && (R * NPT) % 8 == 0;
+#define SCAN_CASE(K, Y)                                                                                                    \
     case K: {                                                                                                              \
         static size_t configured = 0;                                                                                      \
         if (smem > 48 * 1024 && smem > configured) {                                                                       \
-            cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel<T, K, Y>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (err != cudaSuccess) return (int)err;                                                                       \
             configured = smem;                                                                                             \
         }                                                                                                                  \
-        return (int)launch_kernel(ssm_scan_kernel<T, K>, grid, threads, smem, stream, xbc, xbc_stride, dt, dt_stride, dt_bias, \
+        return (int)launch_kernel(ssm_scan_kernel<T, K, Y>, grid, threads, smem, stream, xbc, xbc_stride, dt, dt_stride, dt_bias, \
                                   a_log, d_skip, state, slot_stride, y, meta, cu_tokens, slots, heads, P, N, groups, R, pass,  \
-                                  chunk_len, max_chunks, scratch, decay);                                                  \
+                                  chunk_len, max_chunks, scratch, decay, vec8);                                            \
     }
-    switch (NPT) {
-        SCAN_CASE(16) SCAN_CASE(24) SCAN_CASE(32) SCAN_CASE(48) SCAN_CASE(64)
+    if (pass == 1) {  // chunks that only leave their end state: no y, a third less arithmetic
+        switch (NPT) { SCAN_CASE(16, false) SCAN_CASE(24, false) SCAN_CASE(32, false) SCAN_CASE(48, false) SCAN_CASE(64, false) }
+    } else {
+        switch (NPT) { SCAN_CASE(16, true) SCAN_CASE(24, true) SCAN_CASE(32, true) SCAN_CASE(48, true) SCAN_CASE(64, true) }
     }
 #undef SCAN_CASE
     return (int)cudaErrorInvalidValue;
@@ -306,6 +439,27 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
     const float* yr = y + (size_t)t * n + at;
     const T* zr = z + (size_t)t * z_stride + at;
     float ss = 0.f;
+    if (len <= 8 * (int)blockDim.x) {  // the gated values wait in registers for the sum: y and z are read once
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            v[k] = 0.f;
+            if (i < len) {
+                const float g = to_float(zr[i]);
+                v[k] = yr[i] * (g / (1.f + expf(-g)));
+            }
+            ss = fmaf(v[k], v[k], ss);
+        }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)len + eps);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < len) out[(size_t)t * n + at + i] = from_float<T>(v[k] * inv * w[at + i]);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < len; i += blockDim.x) {
         const float g = to_float(zr[i]);
         const float v = yr[i] * (g / (1.f + expf(-g)));

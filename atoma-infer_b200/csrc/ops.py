@@ -471,6 +471,8 @@ class CudaOps:
                                                      _p(self.status), self._stream()), "attn_decode_flat")
                     return
                 seen = min(ctx.max_context, chunk) if chunk else ctx.max_context  # most keys a request reads
+                if window:
+                    seen = min(seen, window)
                 splits = self.decode_splits(S, nkv, seen, lib.attn_decode_blocks_per_sm())
                 # the splits merge inside a thread-block cluster when they fit one, else through scratch
                 if S <= SKINNY_MAX_ROWS:
@@ -551,17 +553,22 @@ class CudaOps:
         self._check(self._mixers().activation_rows(_p(z), _p(out), _code(z), _p(meta), z.shape[0], z.shape[1], code,
                                                    self._stream()), "activation_rows")
 
-    def causal_conv_act(self, u, w, bias, state, ctx, out, *, act: str = "silu"):
+    def causal_conv_act(self, u, w, bias, state, ctx, out, *, act: str = "silu") -> bool:
         """out[t] = act(bias + sum_j w[j] * u[t - taps + 1 + j]) over the rows of each request, zeros before its start; ``u``
         a slice of wider rows, ``w`` float32 [taps, C], ``bias`` float32 [C] or None; rows before the step's portion come
-        from ``state`` (float32 [slots, taps - 1, C], the row of position p at place p mod (taps - 1)), which
-        ``causal_conv_save`` writes afterwards."""
+        from ``state`` (float32 [slots, taps - 1, C], the row of position p at place p mod (taps - 1)).  Returns whether
+        the state has been updated too (decode steps, where the thread that read a channel's ring also owns the new
+        row's place); if not, ``causal_conv_save`` writes it afterwards."""
         taps, C = w.shape
         up, us = self._rows(u, "causal_conv_act")
-        self._check(self._mixers().causal_conv_act(up, _code(u), us, _p(w), _p(bias), _p(state), self._slot_stride(state), _p(out),
-                                                   _p(ctx.meta), _p(ctx.positions), _p(ctx.token_entry), _p(ctx.cu_tokens),
-                                                   _p(ctx.state_slots), ctx.T, C, taps, {"none": 0, "silu": 1}[act],
-                                                   self._stream()), "causal_conv_act")
+        lib = self._mixers()
+        saves = bool(taps > 1 and ctx.decode_only and ctx.T == ctx.S and
+                     lib.causal_conv_act_saves(up, _code(u), us, _p(w), _p(bias), _p(state), self._slot_stride(state), _p(out), C))
+        self._check(lib.causal_conv_act(up, _code(u), us, _p(w), _p(bias), _p(state), self._slot_stride(state), _p(out),
+                                        _p(ctx.meta), _p(ctx.positions), _p(ctx.token_entry), _p(ctx.cu_tokens),
+                                        _p(ctx.state_slots), ctx.T, C, taps, {"none": 0, "silu": 1}[act], int(saves),
+                                        self._stream()), "causal_conv_act")
+        return saves or taps == 1
 
     def causal_conv_save(self, u, state, ctx, taps: int):
         """The last taps - 1 rows of u of every entry go to its state (see ``causal_conv_act``)."""
@@ -653,24 +660,53 @@ class CudaOps:
         self._check(self._mixers().moe_route(_p(h), _code(h), _p(w_router), _p(ids), _p(wts), _p(meta), h.shape[0], H, E,
                                              ids.shape[1], self._stream()), "moe_route")
 
+    MOE_PAIR_ROWS = 64       # up to this many (token, choice) pairs, bfloat16: a pair at a time
+    MOE_LIBRARY_ROWS = 256   # from this many pairs on, bfloat16: the library's grouped products
+    moe_library = hasattr(torch, "_grouped_mm")  # (a test lever too)
+
     def moe_experts(self, h, ids, wts, w_gate_up, w_down, shared, out, meta):
         """out[t] = sum_k wts[t, k] * expert ids[t, k] of h[t] (+ shared[t]); an expert is down(silu(gate x) * up x) with
         ``w_gate_up`` [E, 2F, H] (gate rows first) and ``w_down`` [E, H, F].  The (token, choice) pairs are sorted by expert
-        on the device and the two linears run as grouped products over that order."""
+        on the device and the two linears run as grouped products over that order: on the engine's own tile kernel
+        (float32 always: every output's order of summation is then the same for any batch), or, in bfloat16, a pair at a
+        time for a handful of pairs and through the library's grouped product for many."""
         T, top = ids.shape
         E, F2, H = w_gate_up.shape
         F = F2 // 2
         lib, dev = self._mixers(), h.device
+        pairs, bf = T * top, h.dtype == torch.bfloat16
+        act = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+        if bf and pairs <= self.MOE_PAIR_ROWS and H % 8 == 0 and F % 8 == 0 and max(H, F) * 2 <= 96 * 1024:
+            # a handful of pairs (decode steps): every pair streams its expert's rows itself, no sorting
+            y = torch.empty((pairs, H), dtype=torch.float32, device=dev)
+            self._check(lib.moe_pair_ff(_p(h), _p(w_gate_up), _p(act), _p(w_down), _p(y), _p(ids), _p(meta), T, top, H, F,
+                                        self._stream()), "moe_pair_ff")
+            self.launches += 1
+            self._check(lib.moe_combine(_p(y), DT_F32, None, _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top, H,
+                                        self._stream()), "moe_combine")
+            return
         offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
-        order = torch.empty(T * top, dtype=torch.int32, device=dev)
-        self._check(lib.moe_sort(_p(ids), _p(offsets), _p(order), _p(meta), top, E, self._stream()), "moe_sort")
-        act = torch.empty((T * top, F), dtype=h.dtype, device=dev)
-        y = torch.empty((T * top, H), dtype=torch.float32, device=dev)
+        order = torch.empty(pairs, dtype=torch.int32, device=dev)
+        place = torch.empty(pairs, dtype=torch.int32, device=dev)
+        self._check(lib.moe_sort(_p(ids), _p(offsets), _p(order), _p(place), _p(meta), top, E, self._stream()), "moe_sort")
+        if bf and pairs >= self.MOE_LIBRARY_ROWS and self.moe_library and H % 8 == 0 and F % 8 == 0:
+            # many pairs: rows gathered in sorted order, the two products as the library's grouped products over the
+            # experts' stretches (offsets on the device: no host round trip), like the many-row linears
+            xs = torch.empty((pairs, H), dtype=h.dtype, device=dev)
+            self._check(lib.moe_gather_rows(_p(h), _p(xs), _p(order), _p(meta), T, top, H * 2, self._stream()), "moe_gather_rows")
+            ends = offsets[1:]
+            gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)
+            self.silu_mul(gu, act, None, pairs, F)
+            y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
+            self._check(lib.moe_combine(_p(y), DT_BF16, _p(place), _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top, H,
+                                        self._stream()), "moe_combine")
+            return
+        y = torch.empty((pairs, H), dtype=torch.float32, device=dev)
         self._check(lib.moe_grouped_ff(_p(h), _p(w_gate_up), _p(act), _p(w_down), _p(y), _p(offsets), _p(order), _code(h), T, top,
                                        E, H, F, self._stream()), "moe_grouped_ff")
         self.launches += 1
-        self._check(lib.moe_combine(_p(y), _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top, H, self._stream()),
-                    "moe_combine")
+        self._check(lib.moe_combine(_p(y), DT_F32, None, _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top, H,
+                                    self._stream()), "moe_combine")
 
     # ------------------------------------------------------------------ whole layers of a decode step
     def _decode_stack_library(self, d: int):

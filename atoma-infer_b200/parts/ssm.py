@@ -96,8 +96,8 @@ class Mamba2Mixer(Mixer):
         z, u, dt = proj[:, :inner], proj[:, inner:inner + self.channels], proj[:, inner + self.channels:]
         ring = self.ring(cache.state)
         xbc = torch.empty((T, self.channels), dtype=x.dtype, device=x.device)
-        ops.causal_conv_act(u, self.conv_w, self.conv_b, ring, ctx, xbc, act="silu")
-        ops.causal_conv_save(u, ring, ctx, self.taps)  # after the convolution has read the ring
+        if not ops.causal_conv_act(u, self.conv_w, self.conv_b, ring, ctx, xbc, act="silu"):
+            ops.causal_conv_save(u, ring, ctx, self.taps)  # after the convolution has read the ring
         y = torch.empty((T, inner), dtype=torch.float32, device=x.device)
         ops.ssm_scan(xbc, dt, self.dt_bias, self.a_log, self.d_skip, self.matrices(cache.state), ctx, y,
                      heads=self.heads, head_dim=self.head_dim, nstate=self.nstate, groups=self.groups)

@@ -246,7 +246,25 @@ def design_configs(size: str, layers: int, vocab: int = 32768, chunk: int = 1024
     return llama, dosovik
 
 
-def design_comparison(args) -> int:
+def tutezen_config(size: str, layers: int, vocab: int = 32768, window: int = 1024):
+    """A Tutezen configuration of the width and feed-forward size of ``size``: state-space layers with a dense
+    feed-forward alternate with latent-attention layers with routed experts (a quarter of the dense size each, two of
+    sixteen chosen, one shared), the middle two layers run twice.  The state-space layers are twice the width inside
+    (heads of 64, a state of 128 rows, 8 groups, 4 taps); latent attention caches 224 + 32 elements a token."""
+    H, I, nq, _, d = DESIGN_SIZES[size]
+    ssm = {"heads": 2 * H // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+    att = {"heads": 16, "dim": d, "rot_dim": 32, "vdim": d, "q_rank": H // 4, "kv_rank": 224, "scale": (d + 32) ** -0.5,
+           "mask": {"size": window}, "rot": {"dims": 32, "base": 500000.0}}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": I // 4}, "shared": {"ff": I // 4}}
+    pair = [{"type": "mamba2", "mixer": ssm, "mlp": {"kind": "dense", "ff": I}}, {"type": "latent_attention", "mixer": att, "mlp": moe}]
+    cfg = {"architecture": "Tutezen", "vocab": vocab, "width": H, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+           "layers": [pair[i % 2] for i in range(layers)]}
+    if layers >= 4:
+        cfg["loop"] = {"start": layers // 2 - 1, "stop": layers // 2 + 1, "times": 2}
+    return cfg
+
+
+def design_comparison(args, other: str = "dosovik") -> int:
     """Prefill (one prompt of 2,048 tokens) and decode (8 requests, 2,048 tokens cached each, captured graphs)
     through the step function for both designs at each size; then single kernels.  Timing: CUDA events, the median
     of five regions after three warm-up runs; weights and activations of a step exceed the L2 at every size."""
@@ -275,7 +293,10 @@ def design_comparison(args) -> int:
 
     rows = []
     for size in DESIGN_SIZES:
-        for name, cfg in zip(("llama", "dosovik"), design_configs(size, layers)):
+        pairs = design_configs(size, layers)
+        if other == "tutezen":  # two layers fewer: the middle two run twice, so a step runs as many layers as Llama's
+            pairs = (pairs[0], tutezen_config(size, max(layers - 2, 2)))
+        for name, cfg in zip(("llama", other), pairs):
             with tempfile.TemporaryDirectory() as d:
                 with open(os.path.join(d, "config.json"), "w") as f:
                     json.dump(cfg, f)
@@ -304,6 +325,11 @@ def design_comparison(args) -> int:
             lm.rt.ops.check_status()
             weights = sum(w.numel() * w.element_size() for r in lm.model.runs for w in lm.model.blocks[r.layer].streamed_weights())
             weights += lm.model.head.weight.numel() * 2
+            for r in lm.model.runs:  # routed experts: a step streams what its tokens choose, at most every expert
+                ff = getattr(lm.model.blocks[r.layer], "feed_forward", None)
+                if hasattr(ff, "w_gate_up") and ff.w_gate_up.dim() == 3:
+                    per = (ff.w_gate_up[0].numel() + ff.w_down[0].numel()) * 2
+                    weights += per * min(ff.experts, batch * ff.top)
             row = {"size": size, "design": name, "layers": layers, "prefill_tokens": prefill, "prefill_ms": round(pre_ms, 3),
                    "prefill_tok_s": round(prefill / pre_ms * 1e3), "decode_batch": batch, "context": ctx_len,
                    "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3),
@@ -313,7 +339,7 @@ def design_comparison(args) -> int:
             print(json.dumps(row), flush=True)
             del lm
             torch.cuda.empty_cache()
-    design_kernels(make_runtime("bfloat16", "cuda:0"), hbm, median_ms)
+    (tutezen_kernels if other == "tutezen" else design_kernels)(make_runtime("bfloat16", "cuda:0"), hbm, median_ms)
     return 0
 
 
@@ -397,6 +423,133 @@ def design_kernels(rt, hbm, median_ms) -> None:
                          ("dosovik: attention, sink alone", {"sink": True})):
             us = graph_us(lambda: ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, 0, 0.125, **kw), n=4)
             print(f"  {name:62s} {T:5d} rows {us:8.1f} us")
+    ops.check_status()
+
+
+def _graph_us(fn, n=16):
+    """Microseconds a call: n calls captured in one CUDA graph, CUDA events around three replays, after three warm-up calls."""
+    import torch
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        for _ in range(n):
+            fn()
+    gr.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(3):
+        gr.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / (3 * n) * 1e3
+
+
+def tutezen_kernels(rt, hbm, median_ms) -> None:
+    """The Tutezen layers' own kernels beside the framework's like kernels, alone, at width 2048 (the sizes of
+    ``tutezen_config("w2048-h64", ...)``): microseconds a call and, for kernels that move bytes, the fraction of the copy
+    bandwidth that the bytes each must move give; for the recurrence and the experts' products, which compute, the rate
+    of their arithmetic.  Rows of 16,384 tokens and of 8 tokens (a decode step: the time of a launch inside a graph)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import kernel_utils as K
+    from atoma_infer_b200.parts.base import PendingSum
+
+    ops, dev, bf = rt.ops, rt.device, torch.bfloat16
+    H, I, taps = 2048, 8192, 4
+    heads, P, N, G = 64, 64, 128, 8
+    inner, C = heads * P, heads * P + 2 * G * N
+    lh, rank, rdim, D = 16, 224, 32, 256
+    E, top, F = 16, 2, 2048
+    print(f"kernels alone (copy bandwidth {hbm:.0f} GB/s): name, rows, us, bytes moved / time / copy bandwidth, or the rate")
+    for T in (16384, 8):
+        entries = [(0, T)] if T > 64 else [(100 + i, 1) for i in range(T)]
+        S = len(entries)
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 0)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        rnd = lambda *shape: torch.randn(*shape, device=dev)  # noqa: E731
+        resid, a, b, w = rnd(T, H), rnd(T, H).to(bf), rnd(T, H).to(bf), torch.ones(H, device=dev)
+        out = torch.empty(T, H, device=dev, dtype=bf)
+        proj = (rnd(T, 2 * inner + 2 * G * N + heads) * 0.5).to(bf)
+        cw, cb, ring = rnd(taps, C), rnd(C), torch.zeros(S, taps - 1, C, device=dev)
+        xbc = torch.empty(T, C, device=dev, dtype=bf)
+        mats = torch.zeros(S, heads, N, P, device=dev)
+        y = torch.empty(T, inner, device=dev)
+        hv = torch.ones(heads, device=dev)
+        g_out, nw = torch.empty(T, inner, device=dev, dtype=bf), torch.ones(inner, device=dev)
+        gu, act = rnd(T, 2 * I).to(bf), torch.empty(T, I, device=dev, dtype=bf)
+        z_up = gu[:, :I].contiguous()
+        qkv = rnd(T, (32 + 16) * 64).to(bf)
+        cache_l = torch.zeros(num_pages, 2, 8, PAGE, 64, device=dev, dtype=bf)
+        inv_freq = torch.ones(32, device=dev)
+        q_rot, q_abs, dkv = rnd(T, lh, 64 + rdim).to(bf), rnd(T, lh, rank).to(bf), rnd(T, rank + rdim).to(bf)
+        cache_t = torch.zeros(num_pages, 2, 1, PAGE, D, device=dev, dtype=bf)
+        q_full = torch.empty(T, lh * D, device=dev, dtype=bf)
+        nrm, fr = torch.ones(rank, device=dev), torch.ones(rdim // 2, device=dev)
+        x = rnd(T, H).to(bf)
+        wr = rnd(E, H) * 0.1
+        ids, wts = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, device=dev)
+        wgu, wdn = (rnd(E, 2 * F, H) * 0.02).to(bf), (rnd(E, H, F) * 0.02).to(bf)
+        dense_gu, dense_dn = (rnd(2 * F * top, H) * 0.02).to(bf), (rnd(H, F * top) * 0.02).to(bf)
+        moe_out = torch.empty(T, H, device=dev, dtype=bf)
+        ops.moe_route(x, wr, ids, wts, ctx.meta)
+        scan_flops = 6.0 * T * heads * N * P * (2 if T >= 128 else 1)  # (chunks of time run twice)
+        ff_flops = 6.0 * T * top * H * F
+        cases = [
+            ("tutezen: pending sum of two + RMSNorm", lambda: ops.sum_rmsnorm(resid, PendingSum((a, b), 0.5), w, 1e-5, out, ctx.meta, T),
+             T * H * (4 + 2 + 2 + 4 + 2), None),
+            ("llama:   add + RMSNorm", lambda: ops.add_rmsnorm(resid, a, w, 1e-5, out, ctx.meta, T), T * H * (4 + 2 + 4 + 2), None),
+            ("tutezen: convolution + bias + SiLU (+ ring)", lambda: (ops.causal_conv_act(proj[:, inner:inner + C], cw, cb, ring, ctx, xbc) or
+                                                                   ops.causal_conv_save(proj[:, inner:inner + C], ring, ctx, taps)),
+             T * C * (2 + 2), None),
+            ("dosovik: short convolution", lambda: ops.short_conv(resid, cw[:, :H].contiguous(), ring[:, :, :H].contiguous(), ctx, out),
+             T * H * (4 + 2), None),
+            ("tutezen: recurrence (float32 FMA)", lambda: ops.ssm_scan(xbc, proj[:, inner + C:], hv, hv * 0, hv, mats, ctx, y, heads=heads,
+                                                                       head_dim=P, nstate=N, groups=G),
+             T * (C * 2 + inner * 4) + 2 * S * heads * N * P * 4, scan_flops),
+            ("tutezen: gate, norm in 8 parts", lambda: ops.gated_group_norm(y, proj[:, :inner], nw, 8, 1e-5, g_out, ctx.meta),
+             T * inner * (4 + 2 + 2), None),
+            ("llama:   SiLU * up", lambda: ops.silu_mul(gu, act, ctx.meta, T, I), T * I * 2 * 3, None),
+            ("tutezen: GELU", lambda: ops.activation(z_up, act, "gelu_tanh", ctx.meta), T * I * 2 * 2, None),
+            ("tutezen: latent rows (norm, rotation, pages, queries)",
+             lambda: ops.latent_rows(q_rot[:, :, 64:], q_abs, dkv, nrm, 1e-5, ctx, cache_t, 0, q_full, heads=lh, kv_rank=rank, rot_dim=rdim,
+                                     padded=D, page_size=PAGE, num_pages=num_pages, store=True, inv_freq=fr, rotary_dims=rdim),
+             T * (lh * (rank + rdim) * 2 + (rank + rdim) * 2 + lh * D * 2 + 2 * D * 2), None),
+            ("llama:   rotation + pages", lambda: ops.rope_kv_store(qkv, ctx.positions, ctx.token_entry, ctx.meta, 0, inv_freq, cache_l, num_pages,
+                                                                    T, 32, 8, 64, 64, PAGE, True), T * 48 * 64 * 2 * 2, None),
+            ("tutezen: linear per head, 64 -> 224 (queries)", lambda: ops.head_linear(q_rot[:, :, :64], wgu[0, :lh * rank, :64].reshape(lh, rank, 64).contiguous(),
+                                                                                  q_abs, ctx.meta), T * lh * (64 + rank) * 2, 2.0 * T * lh * 64 * rank),
+            ("tutezen: router (float32)", lambda: ops.moe_route(x, wr, ids, wts, ctx.meta), T * H * 2, None),
+            ("tutezen: experts (sort, two grouped products, weighted sum)",
+             lambda: ops.moe_experts(x, ids, wts, wgu, wdn, None, moe_out, ctx.meta),
+             min(E, T * top) * 3 * F * H * 2 + T * H * 4, ff_flops),
+            ("llama:   gate/up + SiLU * up, down, at the experts' sizes (dense)",
+             lambda: ops.linear(ops.linear(x, dense_gu, silu_mul=True, meta=ctx.meta), dense_dn, meta=ctx.meta),
+             3 * top * F * H * 2 + T * H * 4, ff_flops),
+        ]
+        for name, fn, nbytes, flops in cases:
+            us = _graph_us(fn, n=16 if T <= 64 else 2)
+            rate = f"  {flops / (us * 1e-6) / 1e12:7.1f} TFLOP/s" if flops else ""
+            print(f"  {name:68s} {T:5d} rows {us:9.1f} us  {nbytes / (us * 1e-6) / (hbm * 1e9):5.2f}{rate}")
+        # attention: a prompt of T tokens (or T decode tokens over 2,048 cached ones)
+        entries = [(0, T)] if T > 64 else [(2047, 1)] * T
+        tables, num_pages = K.scrambled_tables([c + n for c, n in entries], PAGE, 1)
+        ctx, _ = K.make_context(rt, entries, PAGE, tables)
+        sinks = torch.zeros(lh, device=dev)
+        for name, nq, nkv, d, kw in (("llama:   attention, 32 x 64 over 8 x 64", 32, 8, 64, {}),
+                                     ("llama:   attention, window 1024", 32, 8, 64, {"window": 1024}),
+                                     ("tutezen: latent attention, 16 x 256 over 1 x 256, window 1024 + sinks", lh, 1, D, {"window": 1024, "sink": sinks})):
+            cache = torch.randn(num_pages, 2, nkv, PAGE, d, device=dev).to(bf)
+            q, o = torch.randn(T, nq * d, device=dev).to(bf), torch.empty(T, nq * d, device=dev, dtype=bf)
+            window = kw.pop("window", 0)
+            us = _graph_us(lambda: ops.attention(q, nq * d, cache, ctx, 0, o, nq, nkv, d, PAGE, num_pages, window, 0.125, **kw), n=4)
+            keys = min(window, T) if window else T
+            flops = 4.0 * T * nq * d * (keys / (1 if window and T > window else 2) if T > 64 else min(window or 2048, 2048))
+            print(f"  {name:68s} {T:5d} rows {us:9.1f} us         {flops / (us * 1e-6) / 1e12:7.1f} TFLOP/s")
     ops.check_status()
 
 
@@ -507,6 +660,9 @@ def main() -> int:
     ap.add_argument("--designs", action="store_true",
                     help="instead of the benchmark: prefill and decode throughput of the Dosovik design beside Llama at equal "
                          "layer sizes (a JSON line each), then the design's kernels alone beside Llama's like kernels")
+    ap.add_argument("--tutezen", action="store_true",
+                    help="instead of the benchmark: prefill and decode throughput of the Tutezen design beside Llama at equal "
+                         "width and as many layer runs (a JSON line each), then the design's kernels alone beside like kernels")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="measure only one phase (for profiling); the JSON line then lacks the other")
     args = ap.parse_args()
@@ -525,6 +681,8 @@ def main() -> int:
         return few_row_linears(args.model)
     if args.designs:
         return design_comparison(args)
+    if args.tutezen:
+        return design_comparison(args, other="tutezen")
     if args.model != "1b":
         return serving_workload(args.model)
 

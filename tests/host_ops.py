@@ -230,6 +230,7 @@ class HostOps:
             rows = torch.cat([torch.stack(past), u[a:b].float()]) if past else u[a:b].float()
             y = PT.causal_conv(rows, wt.float(), bias if bias is not None else torch.zeros(wt.shape[0]))[len(past):]
             out[a:b] = (PT.silu(y) if act == "silu" else y).to(out.dtype)
+        return taps == 1  # the state is left to causal_conv_save
 
     def causal_conv_save(self, u, state, ctx, taps):
         self._count()
