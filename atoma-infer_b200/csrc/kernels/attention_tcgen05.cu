@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(TC_THREADS, HEAD_DIM == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, int q_stride,
                        CacheLayout L, const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                        const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, int chunk_arg, int sink_arg,
-                       float scale_log2, int num_pages, int bt_cap, int* __restrict__ status) {
+                       const float* __restrict__ sink_values, float scale_log2, int num_pages, int bt_cap,
+                       int* __restrict__ status) {
     const int chunk = CS ? chunk_arg : 0, sink = CS ? sink_arg : 0;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -365,9 +366,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         constexpr int DH = D / 2;  // my half of the head
         // m_run: the row's maximum so far; m_base: the base of the exponentials, which follows it lazily;
         // l_run: the sum over my half of the keys, in units of 2^m_base (the halves add up at the end)
-        // sink: one more key of score 0 without a value; maximum and base start there, and one of the row's two
-        // threads starts its sum with the sink's term
-        float m_run = sink ? 0.f : -INFINITY, m_base = m_run, l_run = sink && half == 0 ? 1.f : 0.f;
+        // sink: one more key without a value, of score 0 or of the head's learned score (which no scale touches);
+        // maximum and base start there, and one of the row's two threads starts its sum with the sink's term
+        float m_run = sink ? (CS && sink_values ? sink_values[kvh * G + my_hd] * LOG2E : 0.f) : -INFINITY, m_base = m_run,
+              l_run = sink && half == 0 ? 1.f : 0.f;
         // the first key my row sees: its window's or its chunk's start
         int my_lo = window > 0 ? my_pos - window + 1 : 0;
         if (chunk > 0 && my_pos >= 0) my_lo = max(my_lo, my_pos - my_pos % chunk);
@@ -525,10 +527,11 @@ extern "C" int attn_prefill_tc_supports(int page_size, int nq, int nkv) {
     return ps_ok && nq % nkv == 0 && nq / nkv <= 16;
 }
 
-extern "C" int attn_prefill_tc_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                                      const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
-                                      int nkv, int page_size, int num_pages, int window, int chunk, int sink, float scale,
-                                      int max_context, int* status, cudaStream_t stream) {
+// sink_values (one float per query head, or null): the sink's score per head instead of 0.
+extern "C" int attn_prefill_tc_sinks(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                     const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
+                                     int nkv, int page_size, int num_pages, int window, int chunk, int sink,
+                                     const float* sink_values, float scale, int max_context, int* status, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
     if (!attn_prefill_tc_supports(page_size, nq, nkv)) return (int)cudaErrorInvalidValue;
     EncodeTiledFn fn = encode_fn();
@@ -561,13 +564,21 @@ extern "C" int attn_prefill_tc_masked(const void* q, int q_stride, const void* c
     dim3 grid(nkv, (max_q_len + tpt - 1) / tpt, S);
     if (cs)
         attn_prefill_tc_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens,
-                                                                  ctx_lens, (bf16*)out, nq, window, chunk, sink, scale * LOG2E,
-                                                                  num_pages, bt_cap, status);
+                                                                  ctx_lens, (bf16*)out, nq, window, chunk, sink, sink_values,
+                                                                  scale * LOG2E, num_pages, bt_cap, status);
     else
         attn_prefill_tc_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map, (const bf16*)q, q_stride, L, meta, group, cu_tokens,
-                                                                   ctx_lens, (bf16*)out, nq, window, 0, 0, scale * LOG2E,
+                                                                   ctx_lens, (bf16*)out, nq, window, 0, 0, nullptr, scale * LOG2E,
                                                                    num_pages, bt_cap, status);
     LAUNCH_RETURN();
+}
+
+extern "C" int attn_prefill_tc_masked(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                      const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq,
+                                      int nkv, int page_size, int num_pages, int window, int chunk, int sink, float scale,
+                                      int max_context, int* status, cudaStream_t stream) {
+    return attn_prefill_tc_sinks(q, q_stride, cache, meta, group, cu_tokens, ctx_lens, out, S, max_q_len, nq, nkv, page_size,
+                                 num_pages, window, chunk, sink, nullptr, scale, max_context, status, stream);
 }
 
 extern "C" int attn_prefill_tc(const void* q, int q_stride, const void* cache, const int* meta, int group,

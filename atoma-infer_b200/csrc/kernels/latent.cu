@@ -148,33 +148,62 @@ extern "C" int sigmoid_gate(void* y, long long ys_t, long long ys_h, const void*
 // goes to the key plane and to the value plane of the token's page (one key/value head of D elements); the queries
 // become [q_abs[h] | rotated q_rot[h] | zeros] of D elements a head.  Rotation: of the first `rot` dimensions of a
 // rotated part, 2i pairs with 2i + 1, by the angle position * inv_freq[i] (float32 product, sincosf).
-// One block per (token, query head), and one more per token (block y = heads) for the cached vector.
+// Two neighbouring elements at once (the address a multiple of two elements): a rotation's pair.
+__device__ __forceinline__ void load2(const float* p, float& a, float& b) { const float2 t = *reinterpret_cast<const float2*>(p); a = t.x; b = t.y; }
+__device__ __forceinline__ void load2(const __nv_bfloat16* p, float& a, float& b) {
+    const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    a = t.x; b = t.y;
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+
+// A block takes one token and `hpb` of its heads + 1 jobs: job h < heads lays out query head h, job `heads` makes the
+// cached vector.  Few tokens: a job a block; many: all of a token's jobs in one block, which takes the cosines and
+// sines once.  `pairs`: sizes, strides and addresses are even, so a thread takes a rotation's pair with one access.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_rows_kernel(const T* __restrict__ q_rot, long long qs_t, long long qs_h, const T* __restrict__ q_abs,
                    const T* __restrict__ dkv, long long dkv_stride, const float* __restrict__ norm_w, float eps,
                    const int* __restrict__ positions, const int* __restrict__ token_entry, const int* __restrict__ meta,
                    int group, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out, T* __restrict__ cache,
-                   int heads, int rank, int rdim, int D, int page_size, int num_pages, int store, int* __restrict__ status) {
+                   int heads, int rank, int rdim, int D, int page_size, int num_pages, int store, int pairs, int hpb,
+                   int* __restrict__ status) {
     __shared__ float red[33];
     extern __shared__ float cs[];  // rot / 2 cosines, rot / 2 sines
     float* sn = cs + rot / 2;
     // The step's metadata is written by no kernel of the step: it is read before the wait.
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    const bool live = t < meta[META_NUM_TOKENS] && (h < heads || store);
+    const int t = blockIdx.x, h_first = blockIdx.y * hpb, h_end = min(heads + (store ? 1 : 0), h_first + hpb), tid = threadIdx.x;
+    const bool live = t < meta[META_NUM_TOKENS] && h_first < h_end;
     const int p = live ? positions[t] : 0;
     int page = 0;
-    if (live && h == heads) page = (meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group])[p / page_size];
+    if (live && h_end == heads + 1) page = (meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group])[p / page_size];
     if (live)
         for (int i = tid; i < rot / 2; i += blockDim.x) sincosf((float)p * inv_freq[i], &sn[i], &cs[i]);
     pdl_wait();
     pdl_launch_dependents();
     if (!live) return;
     __syncthreads();  // the cosines and sines are written
-    if (h < heads) {
+    for (int h = h_first; h < min(h_end, heads); ++h) {
         const T* qr = q_rot + (size_t)t * qs_t + (size_t)h * qs_h;
         const T* qa = q_abs + ((size_t)t * heads + h) * rank;
         T* dst = q_out + ((size_t)t * heads + h) * D;
+        if (pairs) {
+            for (int i = tid * 2; i < D; i += blockDim.x * 2) {
+                float a = 0.f, b = 0.f;
+                if (i < rank) {
+                    load2(qa + i, a, b);
+                } else if (i < rank + rdim) {
+                    const int j = i - rank;
+                    load2(qr + j, a, b);
+                    if (j < rot) {
+                        const float a0 = a, b0 = b;
+                        rotate_pair(a0, b0, cs[j >> 1], sn[j >> 1], a, b);
+                    }
+                }
+                store2(dst + i, a, b);
+            }
+            continue;
+        }
         for (int i = tid; i < D; i += blockDim.x) {
             float v = 0.f;
             if (i < rank) {
@@ -191,8 +220,8 @@ latent_rows_kernel(const T* __restrict__ q_rot, long long qs_t, long long qs_h, 
             }
             dst[i] = from_float<T>(v);
         }
-        return;
     }
+    if (h_end != heads + 1) return;
     const T* kv = dkv + (size_t)t * dkv_stride;
     float ss = 0.f;
     for (int i = tid; i < rank; i += blockDim.x) {
@@ -208,6 +237,26 @@ latent_rows_kernel(const T* __restrict__ q_rot, long long qs_t, long long qs_h, 
     CacheLayout L{1, page_size, D};
     T* kdst = cache + L.offset(page, 0, 0, p % page_size);
     T* vdst = cache + L.offset(page, 1, 0, p % page_size);
+    if (pairs) {
+        for (int i = tid * 2; i < D; i += blockDim.x * 2) {
+            float a = 0.f, b = 0.f;
+            if (i < rank) {
+                load2(kv + i, a, b);
+                a = a * inv * norm_w[i];
+                b = b * inv * norm_w[i + 1];
+            } else if (i < rank + rdim) {
+                const int j = i - rank;
+                load2(kv + i, a, b);
+                if (j < rot) {
+                        const float a0 = a, b0 = b;
+                        rotate_pair(a0, b0, cs[j >> 1], sn[j >> 1], a, b);
+                    }
+            }
+            store2(kdst + i, a, b);
+            store2(vdst + i, a, b);
+        }
+        return;
+    }
     for (int i = tid; i < D; i += blockDim.x) {
         float v = 0.f;
         if (i < rank) {
@@ -236,14 +285,19 @@ extern "C" int latent_rows(const void* q_rot, long long qs_t, long long qs_h, co
     if (T <= 0) return 0;
     if (rot % 2 || rot > rdim || rank + rdim > D || (rot && !inv_freq)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)rot * sizeof(float);
+    const int elem = dtype == DT_F32 ? 4 : 2;
+    const int pairs = rank % 2 == 0 && rdim % 2 == 0 && D % 2 == 0 && qs_t % 2 == 0 && qs_h % 2 == 0 && dkv_stride % 2 == 0 &&
+                      (((uintptr_t)q_rot | (uintptr_t)q_abs | (uintptr_t)dkv | (uintptr_t)q_out | (uintptr_t)cache) % (2 * elem)) == 0;
+    const int hpb = T >= 512 ? heads + 1 : 1, threads = hpb > 1 ? 256 : 128;
+    const dim3 grid(T, (heads + 1 + hpb - 1) / hpb);
     if (dtype == DT_F32)
-        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<float>, dim3(T, heads + 1), 128, smem, stream, (const float*)q_rot, qs_t,
+        return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<float>, grid, threads, smem, stream, (const float*)q_rot, qs_t,
                                       qs_h, (const float*)q_abs, (const float*)dkv, dkv_stride, norm_w, eps, positions, token_entry,
                                       meta, group, inv_freq, rot, (float*)q_out, (float*)cache, heads, rank, rdim, D, page_size,
-                                      num_pages, store, status);
-    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<__nv_bfloat16>, dim3(T, heads + 1), 128, smem, stream,
+                                      num_pages, store, pairs, hpb, status);
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, latent_rows_kernel<__nv_bfloat16>, grid, threads, smem, stream,
                                   (const __nv_bfloat16*)q_rot, qs_t, qs_h, (const __nv_bfloat16*)q_abs, (const __nv_bfloat16*)dkv,
                                   dkv_stride, norm_w, eps, positions, token_entry, meta, group, inv_freq, rot,
                                   (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, heads, rank, rdim, D, page_size, num_pages, store,
-                                  status);
+                                  pairs, hpb, status);
 }

@@ -191,12 +191,9 @@ extern "C" int causal_conv_save(const void* u, int dtype, long long u_stride, fl
 __device__ __forceinline__ void stage8(const __nv_bfloat16* src, float* dst) {
     const uint4 v = *reinterpret_cast<const uint4*>(src);
     const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(p[i]);
-        dst[2 * i] = f.x;
-        dst[2 * i + 1] = f.y;
-    }
+    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]), d = __bfloat1622float2(p[3]);
+    *reinterpret_cast<float4*>(dst) = make_float4(a.x, a.y, b.x, b.y);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(c.x, c.y, d.x, d.y);
 }
 __device__ __forceinline__ void stage8(const float* src, float* dst) {
     *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
@@ -211,7 +208,10 @@ ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__
                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads, int P, int N, int groups, int R,
                 int pass, int chunk_len, int max_chunks, float* __restrict__ scratch, float* __restrict__ decay, int vec8) {
     extern __shared__ __align__(16) float sm[];
-    const int NP = R * NPT;                 // padded N
+    // A token's B (and C) in shared memory: R slices of NPT rows, one a thread of a column; with several slices each
+    // starts four floats later than the rows alone would put it, so that the R addresses a warp reads at once fall
+    // into different banks.  Row n lies at (n / NPT) * SL + n % NPT.
+    const int SL = R > 1 ? NPT + 4 : NPT, NL = R * NPT, NP = R * SL;
     float* Bs = sm;                         // [SCAN_TT][NP]
     float* Cs = Bs + SCAN_TT * NP;          // [SCAN_TT][NP]
     float* xs = Cs + SCAN_TT * NP;          // [SCAN_TT][P]
@@ -249,23 +249,24 @@ ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__
             for (int tt = warp; tt < nt; tt += nwarps) {
                 const T* row = xbc + (size_t)(tb + tt) * xbc_stride;
                 const T* brow = row + inner + (size_t)g * N;
-                for (int n = lane * 8; n < NP; n += 256) {
+                for (int n = lane * 8; n < NL; n += 256) {
+                    const int at = tt * NP + (n / NPT) * SL + n % NPT;
                     if (n < N) {
-                        stage8(brow + n, Bs + tt * NP + n);
-                        stage8(brow + (size_t)groups * N + n, Cs + tt * NP + n);
+                        stage8(brow + n, Bs + at);
+                        stage8(brow + (size_t)groups * N + n, Cs + at);
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) Bs[tt * NP + n + i] = Cs[tt * NP + n + i] = 0.f;
+                        for (int i = 0; i < 8; ++i) Bs[at + i] = Cs[at + i] = 0.f;
                     }
                 }
                 for (int q = lane * 8; q < P; q += 256) stage8(row + (size_t)h * P + q, xs + tt * P + q);
             }
         } else {
-            for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
-                const int tt = idx / NP, n = idx % NP;
+            for (int idx = tid; idx < nt * NL; idx += blockDim.x) {
+                const int tt = idx / NL, n = idx % NL, at = tt * NP + (n / NPT) * SL + n % NPT;
                 const T* row = xbc + (size_t)(tb + tt) * xbc_stride + inner + (size_t)g * N;
-                Bs[idx] = n < N ? to_float(row[n]) : 0.f;
-                Cs[idx] = n < N ? to_float(row[(size_t)groups * N + n]) : 0.f;
+                Bs[at] = n < N ? to_float(row[n]) : 0.f;
+                Cs[at] = n < N ? to_float(row[(size_t)groups * N + n]) : 0.f;
             }
             for (int idx = tid; idx < nt * P; idx += blockDim.x) {
                 const int tt = idx / P, q = idx % P;
@@ -282,8 +283,8 @@ ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__
         for (int tt = 0; tt < nt; ++tt) {
             const float xv = real ? xs[tt * P + p] : 0.f, step = dts[tt], dec = decs[tt];
             const float dx = step * xv;
-            const float* Bt = Bs + tt * NP + r * NPT;
-            const float* Ct = Cs + tt * NP + r * NPT;
+            const float* Bt = Bs + tt * NP + r * SL;
+            const float* Ct = Cs + tt * NP + r * SL;
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < NPT; i += 4) {
@@ -405,7 +406,7 @@ extern "C" int ssm_scan(const void* xbc, int dtype, int xbc_stride, const void* 
     int R = 0, NPT = 0;
     if (heads % groups || !scan_geometry(N, P, &R, &NPT)) return (int)cudaErrorInvalidValue;
     const int threads = ((P * R + 31) / 32) * 32;
-    const size_t smem = (size_t)(2 * SCAN_TT * R * NPT + SCAN_TT * P + 2 * SCAN_TT) * sizeof(float);
+    const size_t smem = (size_t)(2 * SCAN_TT * R * (R > 1 ? NPT + 4 : NPT) + SCAN_TT * P + 2 * SCAN_TT) * sizeof(float);
     float* decay = scratch ? scratch + (size_t)S * max_chunks * heads * (size_t)N * P : nullptr;
 #define SCAN_PASS(TT, pass, chunks)                                                                                        \
     ssm_scan_launch<TT>(NPT, dim3(heads, S, chunks), threads, smem, stream, (const TT*)xbc, xbc_stride, (const TT*)dt, dt_stride, \
@@ -430,7 +431,7 @@ extern "C" int ssm_scan(const void* xbc, int dtype, int xbc_stride, const void* 
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride, const float* __restrict__ w,
-                        float eps, T* __restrict__ out, const int* __restrict__ meta, int n, int parts) {
+                        float eps, T* __restrict__ out, const int* __restrict__ meta, int n, int parts, int vec4) {
     __shared__ float red[33];
     pdl_wait();
     pdl_launch_dependents();
@@ -439,6 +440,39 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
     const float* yr = y + (size_t)t * n + at;
     const T* zr = z + (size_t)t * z_stride + at;
     float ss = 0.f;
+    if (vec4 && len <= 8 * (int)blockDim.x) {  // the same, four consecutive values a thread and 16-byte accesses
+        float v[2][4];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = (threadIdx.x + k * blockDim.x) * 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[k][j] = 0.f;
+            if (i < len) {
+                float yv[4], zv[4];
+                load4(yr + i, yv);
+                load4(zr + i, zv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[k][j] = yv[j] * (zv[j] / (1.f + expf(-zv[j])));
+                    ss = fmaf(v[k][j], v[k][j], ss);
+                }
+            }
+        }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)len + eps);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = (threadIdx.x + k * blockDim.x) * 4;
+            if (i < len) {
+                float wv[4];
+                load4(w + at + i, wv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[j] = v[k][j] * inv * wv[j];
+                store4(out + (size_t)t * n + at + i, wv);
+            }
+        }
+        return;
+    }
     if (len <= 8 * (int)blockDim.x) {  // the gated values wait in registers for the sum: y and z are read once
         float v[8];
 #pragma unroll
@@ -479,9 +513,11 @@ extern "C" int gated_group_norm(const float* y, const void* z, int dtype, long l
     if (T <= 0) return 0;
     if (parts <= 0 || n % parts) return (int)cudaErrorInvalidValue;
     const int len = n / parts, threads = len >= 1024 ? 256 : 128;
+    // four values per access: parts and rows start on multiples of four elements and the buffers on 16 bytes
+    const int vec4 = len % 4 == 0 && z_stride % 4 == 0 && (((uintptr_t)y | (uintptr_t)z | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
     if (dtype == DT_F32)
         return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, gated_group_norm_kernel<float>, dim3(T, parts), threads, 0, stream, y,
-                                      (const float*)z, z_stride, w, eps, (float*)out, meta, n, parts);
+                                      (const float*)z, z_stride, w, eps, (float*)out, meta, n, parts, vec4);
     return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, gated_group_norm_kernel<__nv_bfloat16>, dim3(T, parts), threads, 0, stream,
-                                  y, (const __nv_bfloat16*)z, z_stride, w, eps, (__nv_bfloat16*)out, meta, n, parts);
+                                  y, (const __nv_bfloat16*)z, z_stride, w, eps, (__nv_bfloat16*)out, meta, n, parts, vec4);
 }

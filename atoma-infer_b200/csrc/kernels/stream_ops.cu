@@ -130,33 +130,42 @@ __device__ __forceinline__ float gelu_tanh(float z) {
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-activation_kernel(const T* __restrict__ z, T* __restrict__ out, const int* __restrict__ meta, int n, int kind) {
+activation_kernel(const T* __restrict__ z, T* __restrict__ out, const int* __restrict__ meta, int n, int kind, int vec) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int V = 16 / sizeof(T);  // elements of a 16-byte access
     const size_t total = (size_t)meta[META_NUM_TOKENS] * n;
-    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (i >= total) return;
-    if (i + 4 <= total && (n % 4 == 0)) {
-        float v[4];
-        load4(z + i, v);
+    if (vec && i + V <= total) {
+        float v[V];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = gelu_tanh(v[k]);
-        store4(out + i, v);
+        for (int k = 0; k < V; k += 4) {
+            float t4[4];
+            load4(z + i + k, t4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[k + j] = gelu_tanh(t4[j]);
+        }
+#pragma unroll
+        for (int k = 0; k < V; k += 4) {
+            const float o4[4] = {v[k], v[k + 1], v[k + 2], v[k + 3]};
+            store4(out + i + k, o4);
+        }
         return;
     }
-    for (size_t k = i; k < total && k < i + 4; ++k) out[k] = from_float<T>(gelu_tanh(to_float(z[k])));
+    for (size_t k = i; k < total && k < i + V; ++k) out[k] = from_float<T>(gelu_tanh(to_float(z[k])));
 }
 
 extern "C" int activation_rows(const void* z, void* out, int dtype, const int* meta, int T, int n, int kind,
                                cudaStream_t stream) {
     if (T <= 0 || n <= 0) return 0;
     if (kind != 0) return (int)cudaErrorInvalidValue;
+    const int V = dtype == DT_F32 ? 4 : 8;
     const size_t total = (size_t)T * n;
-    const unsigned blocks = (unsigned)((total + 1023) / 1024);
-    // four elements a thread need rows that start on multiples of four elements and buffers on 16 bytes
-    if ((((uintptr_t)z | (uintptr_t)out) & 15) != 0 && n % 4 == 0) return (int)cudaErrorMisalignedAddress;
+    const unsigned blocks = (unsigned)((total + 256 * V - 1) / (256 * V));
+    const int vec = (((uintptr_t)z | (uintptr_t)out) & 15) == 0;  // (rows are contiguous: element i of the whole lies at i)
     if (dtype == DT_F32)
-        return (int)launch_kernel(activation_kernel<float>, blocks, 256, 0, stream, (const float*)z, (float*)out, meta, n, kind);
+        return (int)launch_kernel(activation_kernel<float>, blocks, 256, 0, stream, (const float*)z, (float*)out, meta, n, kind, vec);
     return (int)launch_kernel(activation_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)z,
-                              (__nv_bfloat16*)out, meta, n, kind);
+                              (__nv_bfloat16*)out, meta, n, kind, vec);
 }

@@ -488,12 +488,12 @@ class CudaOps:
                                                   window, int(chunk), int(bool(sink)), _p(sinks), ctypes.c_float(scale), splits,
                                                   int(cluster), ctx.max_context, _p(self.status), self._stream()),
                             "attn_decode")
-            elif sinks is None and self._prefill_tc(d, page_size, nq, nkv) is not None:  # (learned sinks: the mma.sync kernel)
+            elif self._prefill_tc(d, page_size, nq, nkv) is not None:
                 tc = self._prefill_tc(d, page_size, nq, nkv)
-                self._check(tc.attn_prefill_tc_masked(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                                      _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
-                                                      page_size, num_pages, window, int(chunk), int(bool(sink)),
-                                                      ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
+                self._check(tc.attn_prefill_tc_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                                     _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                                     page_size, num_pages, window, int(chunk), int(bool(sink)), _p(sinks),
+                                                     ctypes.c_float(scale), ctx.max_context, _p(self.status), self._stream()),
                             "attn_prefill_tc")
             else:
                 self._check(lib.attn_prefill_sinks(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),

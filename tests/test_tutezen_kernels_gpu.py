@@ -272,11 +272,13 @@ def _window_sink_case(rt, entries, nq, d, page, window, sinks, seed=0, stand_out
 
 
 @pytest.mark.parametrize("dtype,fast", [("float32", True), ("bfloat16", True), ("bfloat16", False)])
-@pytest.mark.parametrize("d,nq,page,window", [(48, 3, 4, 21), (112, 2, 8, 64), (64, 6, 16, 40), (272, 2, 8, 33), (32, 20, 4, 0)])
+@pytest.mark.parametrize("d,nq,page,window", [(48, 3, 4, 21), (112, 2, 8, 64), (64, 6, 16, 40), (128, 16, 16, 100), (272, 2, 8, 33),
+                                              (32, 20, 4, 0)])
 def test_window_and_learned_sink_in_prompt_portions(rts, dtype, fast, d, nq, page, window):
     """Portions that start before, at and behind a window's reach, beside single tokens and the first tokens of a
     sequence; for the last query of each request one key towers: the newest key its window has passed, or the oldest it
-    still holds.  Sinks differ from head to head, one of them large enough to take most of the weight."""
+    still holds.  Sinks differ from head to head, one of them large enough to take most of the weight.  (Head sizes 64
+    and 128 with pages of 8 and more: the tcgen05 kernel.)"""
     rt = rts[dtype]
     tol = 2e-5 if dtype == "float32" else 2.5e-2
     W = window or 50
