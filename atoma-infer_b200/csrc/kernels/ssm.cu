@@ -200,8 +200,10 @@ __device__ __forceinline__ void stage8(const float* src, float* dst) {
     *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
 }
 
-template <typename T, int NPT, bool WRITE_Y>
-__global__ void __launch_bounds__(512)
+// BIG: blocks of more than 256 threads (at most 128 registers a thread; else up to 255, which 64 rows of state with their
+// loads in flight need to stay out of local memory).
+template <typename T, int NPT, bool WRITE_Y, bool BIG>
+__global__ void __launch_bounds__(BIG ? 512 : 256)
 ssm_scan_kernel(const T* __restrict__ xbc, int xbc_stride, const T* __restrict__ dt, long long dt_stride,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, float* __restrict__ y, const int* __restrict__ meta,
@@ -341,6 +343,10 @@ ssm_chunk_states_kernel(const float* __restrict__ state, long long slot_stride, 
     }
 }
 
+// The most rows of state a thread keeps (a lever for measurements; 64: all instantiations).
+static int g_scan_max_rows = 64;
+extern "C" void ssm_scan_set_max_rows(int n) { g_scan_max_rows = n; }
+
 // How a head's N rows are dealt out: R threads a column, NPT rows a thread (R * NPT >= N, R a power of two).
 static bool scan_geometry(int N, int P, int* R_out, int* NPT_out) {
     static const int sizes[] = {16, 24, 32, 48, 64};
@@ -351,7 +357,7 @@ static bool scan_geometry(int N, int P, int* R_out, int* NPT_out) {
         if (threads > 512) break;
         for (int k = 0; k < 5; ++k) {
             const int npt = sizes[k];
-            if (R * npt < N) continue;
+            if (R * npt < N || npt > g_scan_max_rows) continue;
             const long cost = (long)R * npt * 8 + (R > 1 ? R : 0);  // padded work first, then the fewest threads a column
             if (best_cost < 0 || cost < best_cost) best_cost = cost, best_r = R, best_npt = npt;
             break;
@@ -375,23 +381,25 @@ static int ssm_scan_launch(int NPT, dim3 grid, int threads, size_t smem, cudaStr
                            int max_chunks, float* scratch, float* decay) {
     // eight elements a load: rows of x, B and C that start on 16 bytes (float32: two loads of four)
     const int vec8 = P % 8 == 0 && N % 8 == 0 && xbc_stride % 8 == 0 && ((uintptr_t)xbc & 15) == 0 && (R * NPT) % 8 == 0;
-#define SCAN_CASE(K, Y)                                                                                                    \
+#define SCAN_CASE(K, Y, B)                                                                                                  \
     case K: {                                                                                                              \
         static size_t configured = 0;                                                                                      \
         if (smem > 48 * 1024 && smem > configured) {                                                                       \
-            cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel<T, K, Y>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel<T, K, Y, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (err != cudaSuccess) return (int)err;                                                                       \
             configured = smem;                                                                                             \
         }                                                                                                                  \
-        return (int)launch_kernel(ssm_scan_kernel<T, K, Y>, grid, threads, smem, stream, xbc, xbc_stride, dt, dt_stride, dt_bias, \
+        return (int)launch_kernel(ssm_scan_kernel<T, K, Y, B>, grid, threads, smem, stream, xbc, xbc_stride, dt, dt_stride, dt_bias, \
                                   a_log, d_skip, state, slot_stride, y, meta, cu_tokens, slots, heads, P, N, groups, R, pass,  \
                                   chunk_len, max_chunks, scratch, decay, vec8);                                            \
     }
+#define SCAN_SIZES(Y, B) switch (NPT) { SCAN_CASE(16, Y, B) SCAN_CASE(24, Y, B) SCAN_CASE(32, Y, B) SCAN_CASE(48, Y, B) SCAN_CASE(64, Y, B) }
     if (pass == 1) {  // chunks that only leave their end state: no y, a third less arithmetic
-        switch (NPT) { SCAN_CASE(16, false) SCAN_CASE(24, false) SCAN_CASE(32, false) SCAN_CASE(48, false) SCAN_CASE(64, false) }
+        if (threads > 256) SCAN_SIZES(false, true) else SCAN_SIZES(false, false)
     } else {
-        switch (NPT) { SCAN_CASE(16, true) SCAN_CASE(24, true) SCAN_CASE(32, true) SCAN_CASE(48, true) SCAN_CASE(64, true) }
+        if (threads > 256) SCAN_SIZES(true, true) else SCAN_SIZES(true, false)
     }
+#undef SCAN_SIZES
 #undef SCAN_CASE
     return (int)cudaErrorInvalidValue;
 }
