@@ -695,12 +695,17 @@ class CudaOps:
             xs = torch.empty((pairs, H), dtype=h.dtype, device=dev)
             self._check(lib.moe_gather_rows(_p(h), _p(xs), _p(order), _p(meta), T, top, H * 2, self._stream()), "moe_gather_rows")
             ends = offsets[1:]
-            gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)
-            self.silu_mul(gu, act, None, pairs, F)
-            y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
-            self._check(lib.moe_combine(_p(y), DT_BF16, _p(place), _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top, H,
-                                        self._stream()), "moe_combine")
-            return
+            try:
+                gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)
+                self.silu_mul(gu, act, None, pairs, F)
+                y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
+            except (RuntimeError, TypeError, NotImplementedError):
+                y = None  # the library refuses these sizes or strides: the engine's own grouped kernel from now on
+                self.moe_library = False
+            if y is not None:
+                self._check(lib.moe_combine(_p(y), DT_BF16, _p(place), _p(wts), _p(shared), _p(out), _code(out), _p(meta), T, top,
+                                            H, self._stream()), "moe_combine")
+                return
         y = torch.empty((pairs, H), dtype=torch.float32, device=dev)
         self._check(lib.moe_grouped_ff(_p(h), _p(w_gate_up), _p(act), _p(w_down), _p(y), _p(offsets), _p(order), _code(h), T, top,
                                        E, H, F, self._stream()), "moe_grouped_ff")

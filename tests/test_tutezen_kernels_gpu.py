@@ -30,7 +30,7 @@ def _err(got, want):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H", [96, 1100])
+@pytest.mark.parametrize("H", [96, 1100, 90])  # (90: rows that do not start on 16 bytes, one value a thread and step)
 def test_pending_sum_and_norm(rts, dtype, H):
     rt = rts[dtype]
     entries = [(0, 5), (3, 1), (7, 4)]
@@ -104,7 +104,7 @@ def test_convolution_over_portions_and_slots(rts, dtype, taps, C, pad):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,P,N,G", [(3, 16, 24, 1), (4, 8, 40, 2), (2, 64, 128, 2), (8, 24, 16, 4), (2, 32, 200, 1)])
+@pytest.mark.parametrize("heads,P,N,G", [(3, 16, 24, 1), (4, 8, 40, 2), (2, 64, 128, 2), (8, 24, 16, 4), (2, 32, 200, 1), (2, 12, 20, 1)])
 def test_recurrence_in_order_and_in_chunks(rts, dtype, heads, P, N, G):
     """Portions of 1 to 300 tokens beside each other (the long ones run as chunks of time side by side), states in slots
     of a wider per-request state, twice over the same slots: the state is carried, and nothing depends on the cut."""
@@ -148,7 +148,7 @@ def test_recurrence_in_order_and_in_chunks(rts, dtype, heads, P, N, G):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n,parts", [(48, 3), (32, 1), (1280, 2)])
+@pytest.mark.parametrize("n,parts", [(48, 3), (32, 1), (1280, 2), (30, 3), (9000, 1)])
 def test_gated_norm_in_parts(rts, dtype, n, parts):
     rt = rts[dtype]
     g = torch.Generator().manual_seed(n)
@@ -190,7 +190,7 @@ def test_norm_over_a_slice_and_linears_per_head(rts, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,rank,rdim,rot,page", [(3, 48, 8, 8, 4), (2, 20, 16, 6, 8), (5, 32, 16, 0, 16)])
+@pytest.mark.parametrize("heads,rank,rdim,rot,page", [(3, 48, 8, 8, 4), (2, 20, 16, 6, 8), (5, 32, 16, 0, 16), (2, 21, 10, 4, 4)])
 def test_latent_rows(rts, dtype, heads, rank, rdim, rot, page):
     """Queries laid out for the attention kernels, the cached vector on both planes of its page, zeros behind both; the
     rotation pairs neighbours, of the first `rot` rotated dimensions only."""
@@ -198,7 +198,7 @@ def test_latent_rows(rts, dtype, heads, rank, rdim, rot, page):
     tol = 1e-5 if dtype == "float32" else 1e-2
     g = torch.Generator().manual_seed(rank)
     D = -(-(rank + rdim) // 16) * 16
-    entries = [(0, 6), (37, 1), (5, 3)]
+    entries = [(0, 6), (37, 1), (5, 3)] if rank != 32 else [(0, 600), (37, 1), (5, 3)]  # (many tokens: a token a block)
     tables, num_pages = _tables(entries, page)
     ctx, _ = K.make_context(rt, entries, page, tables)
     T = ctx.T
