@@ -11,6 +11,8 @@ fraction of the measured HBM bandwidth.  Prints ONE JSON line.
 
 ``--designs`` instead of the benchmark: prefill and decode throughput of the Dosovik design beside Llama at equal
 layer sizes, and the design's own kernels beside Llama's like kernels with their fractions of the copy bandwidth.
+``--tutezen``: the same for the Tutezen design (state-space and latent-attention layers, routed experts) at Llama's width
+and as many layer runs.
 
 Tables for profiles/ instead of the JSON line: ``--linears [--model 1b|3b|8b]`` (the two few-row linear
 kernels on the four matrices of a layer) and ``--layer-kernel-phases`` (the persistent layer kernel's time
