@@ -120,3 +120,27 @@ def test_the_command_line_serves_the_design(tmp_path):
         args += ["--prompt-ids", ",".join(map(str, p))]
     recs = [json.loads(line) for line in run(args).stdout.splitlines() if line.startswith("{")]
     assert [r["token_ids"] for r in recs] == [TH.plain_greedy(str(out), cfg, p, 8) for p in prompts]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_requests_at_once(dtype, models):
+    """120 requests of unequal length in one go: prompt steps of hundreds of tokens from dozens of requests, then decode
+    steps of 120 rows in captured graphs (the experts' pairs then go through the many-row path inside a graph)."""
+    import plain_tutezen as PT
+    from atoma_infer_b200.engine import Engine
+    from atoma_infer_b200.sampling import SamplingParams
+
+    d, cfg, page = models["R"]
+    prompts = list(helpers.random_tokens(cfg["vocab"], [5 + (i * 7) % 40 for i in range(120)], seed=4).values())
+    eng = Engine(d, dtype=dtype, block_size=page, num_gpu_blocks_override=2000, max_num_sequences=128, max_num_batched_tokens=2048)
+    outs = eng.generate(prompts, SamplingParams(do_sample=False, max_new_tokens=8, ignore_eos_token=True))
+    eng.lm.rt.ops.check_status()
+    assert eng.lm.manager.audit() == "" and eng.lm.manager.num_requests() == 0
+    assert eng.stats()["graph_replays"] > 0
+    w = helpers.read_weights(d)
+    for p, o in list(zip(prompts, outs))[::10]:
+        logits = PT.forward(cfg, w, list(p) + list(o.token_ids))  # each token judged on the engine's own history
+        for i, tok in enumerate(o.token_ids):
+            row = logits[len(p) - 1 + i]
+            lead = float(row.max() - row[tok]) / float(row.abs().max())
+            assert lead <= (2 * helpers.BF16_TOL if dtype == "bfloat16" else 1e-4), (i, tok, lead)
